@@ -1,0 +1,86 @@
+"""ctypes binding of libade_b200.so (the C ABI declared in include/ade_b200.h).
+
+There is no fallback: if the shared object has not been built (``python -m ade_b200.build``)
+loading raises, and every kernel entry raises on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libade_b200.so")
+
+ADE_OK = 0
+ERRORS = {
+    -1: "ADE_ERR_NULL: a required pointer is NULL",
+    -2: "ADE_ERR_SHAPE: a dimension is outside the supported set",
+    -3: "ADE_ERR_ALIGN: a pointer is not 16-byte aligned",
+    -4: "ADE_ERR_SCRATCH: scratch buffer too small",
+    -5: "ADE_ERR_CUDA: a CUDA runtime call failed",
+    -6: "ADE_ERR_DEVICE: the current device is not compute capability 10.x",
+}
+DEVICE_STATUS = {
+    1: "MMA warp timed out waiting for an operand stage",
+    2: "unpack warps timed out waiting for a free operand stage",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "MMA warp timed out waiting for a free accumulator",
+    5: "epilogue timed out waiting for the base-weight tile",
+}
+
+# every symbol include/ade_b200.h declares
+EXPORTS = (
+    "ade_b200_device_status", "ade_b200_version", "ade_b200_last_cuda_error",
+    "ade_b200_pack_codes", "ade_b200_pack_zeros",
+    "ade_b200_factored_scratch_bytes", "ade_b200_factored", "ade_b200_recon",
+)
+
+
+class AdeDelta(ctypes.Structure):
+    """struct ade_delta of include/ade_b200.h."""
+    _fields_ = [
+        ("uq", ctypes.c_void_p), ("vq", ctypes.c_void_p), ("vt", ctypes.c_void_p),
+        ("us", ctypes.c_void_p), ("uz", ctypes.c_void_p), ("vs", ctypes.c_void_p), ("vz", ctypes.c_void_p),
+        ("M", ctypes.c_int), ("N", ctypes.c_int), ("r", ctypes.c_int),
+    ]
+
+
+class AdeKernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the kernel library; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise AdeKernelError(
+            f"{LIB_PATH} is missing: build the CUDA kernels with `python -m ade_b200.build` "
+            "(there is no CPU or PyTorch fallback)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    lib.ade_b200_device_status.restype = ci
+    lib.ade_b200_version.restype = ci
+    lib.ade_b200_last_cuda_error.restype = ci
+    lib.ade_b200_pack_codes.argtypes = [vp, vp, ci, ci, ci, vp]
+    lib.ade_b200_pack_zeros.argtypes = [vp, vp, sz, vp]
+    lib.ade_b200_factored_scratch_bytes.argtypes = [ci, ci]
+    lib.ade_b200_factored_scratch_bytes.restype = sz
+    lib.ade_b200_factored.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp, sz, ci, vp]
+    lib.ade_b200_recon.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp]
+    for name in ("ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_factored", "ade_b200_recon"):
+        getattr(lib, name).restype = ci
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != ADE_OK:
+        extra = ""
+        if rc == -5:
+            extra = f" (cudaError {load().ade_b200_last_cuda_error()})"
+        raise AdeKernelError(f"{what}: {ERRORS.get(rc, rc)}{extra}")

@@ -1,0 +1,207 @@
+// C ABI of the B200 delta-application kernels (declared in include/ade_b200.h).
+// Host side only validates arguments and launches; it never allocates or synchronises.
+#include "../../include/ade_b200.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "factored.cuh"
+#include "recon.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline bool cuda_ok(cudaError_t e) {
+    if (e != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(e);
+        return false;
+    }
+    return true;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+    int ready = 0;      // 1 = usable, -1 = wrong architecture
+    int sms = 0;
+};
+DeviceInfo g_dev[kMaxDevices];
+
+// per-device set-up: architecture check, SM count, dynamic shared-memory opt-in
+int device_info(const DeviceInfo** out) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return ADE_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return ADE_ERR_DEVICE;
+    DeviceInfo& d = g_dev[dev];
+    if (d.ready == 0) {
+        int major = 0, sms = 0;
+        if (!cuda_ok(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev))) return ADE_ERR_CUDA;
+        if (!cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev))) return ADE_ERR_CUDA;
+        if (major != 10) {
+            d.ready = -1;
+        } else {
+            const int smem = static_cast<int>(ade::recon_smem_bytes(ADE_B200_MAX_RANK / 128));
+            if (!cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                return ADE_ERR_CUDA;
+            d.sms = sms;
+            d.ready = 1;
+        }
+    }
+    if (d.ready < 0) return ADE_ERR_DEVICE;
+    *out = &d;
+    return ADE_OK;
+}
+
+int check_delta(const ade_delta_t* d) {
+    if (!d) return ADE_ERR_NULL;
+    if (!d->uq || !d->us || !d->uz || !d->vs || !d->vz) return ADE_ERR_NULL;
+    if (d->M < 1 || d->N < 1 || d->r < ADE_B200_GROUP || d->r > ADE_B200_MAX_RANK) return ADE_ERR_SHAPE;
+    if (d->r % ADE_B200_GROUP || d->N % 128) return ADE_ERR_SHAPE;
+    if (!aligned16(d->uq) || !aligned16(d->us) || !aligned16(d->uz) || !aligned16(d->vs) || !aligned16(d->vz))
+        return ADE_ERR_ALIGN;
+    return ADE_OK;
+}
+
+// ------------------------------------------------------------------ packing kernels
+__global__ void pack_codes_kernel(const uint8_t* __restrict__ codes, uint32_t* __restrict__ out, int rows, int K,
+                                  int transpose) {
+    const size_t words = static_cast<size_t>(rows) * (K >> 3);
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < words;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / (K >> 3);
+        const int k0 = static_cast<int>(i % (K >> 3)) << 3;
+        uint32_t c[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            c[j] = (transpose ? codes[static_cast<size_t>(k0 + j) * rows + row] : codes[row * K + k0 + j]) & 15u;
+        // nibble order c0 c2 c4 c6 c1 c3 c5 c7
+        out[i] = c[0] | (c[2] << 4) | (c[4] << 8) | (c[6] << 12) | (c[1] << 16) | (c[3] << 20) | (c[5] << 24) |
+                 (c[7] << 28);
+    }
+}
+
+__global__ void pack_zeros_kernel(const uint16_t* __restrict__ z, uint8_t* __restrict__ out, size_t count) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[i] = static_cast<uint8_t>(static_cast<int>(ade::bf16_bits_to_f32(z[i])));
+}
+
+template <int NT>
+int launch_factored(const ade_delta_t* d, const __nv_bfloat16* x, const __nv_bfloat16* y_dense,
+                    const __nv_bfloat16* w_b, __nv_bfloat16* out, __nv_bfloat16* h, int T, cudaStream_t st) {
+    ade::xv_kernel<NT><<<d->r / 16, ade::XV_THREADS, 0, st>>>(d->vt, d->vs, d->vz, x, h, T, d->N, d->r);
+    if (!cuda_ok(cudaGetLastError())) return ADE_ERR_CUDA;
+    if (w_b)
+        ade::hu_kernel<NT, true><<<d->M / ade::HU_ROWS, ade::HU_THREADS, 0, st>>>(w_b, x, nullptr, d->uq, d->us, d->uz,
+                                                                                 h, out, T, d->M, d->N, d->r);
+    else
+        ade::hu_kernel<NT, false><<<d->M / ade::HU_ROWS, ade::HU_THREADS, 0, st>>>(nullptr, x, y_dense, d->uq, d->us,
+                                                                                  d->uz, h, out, T, d->M, d->N, d->r);
+    if (!cuda_ok(cudaGetLastError())) return ADE_ERR_CUDA;
+    return ADE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ade_b200_version(void) { return 1; }
+
+int ade_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+int ade_b200_device_status(void) {
+    const DeviceInfo* di = nullptr;
+    return device_info(&di);
+}
+
+int ade_b200_pack_codes(const uint8_t* codes, uint8_t* out, int rows, int K, int transpose, void* stream) {
+    if (!codes || !out) return ADE_ERR_NULL;
+    if (rows < 1 || K < 8 || K % 8) return ADE_ERR_SHAPE;
+    if (!aligned16(out)) return ADE_ERR_ALIGN;
+    const size_t words = static_cast<size_t>(rows) * (K >> 3);
+    const int blocks = static_cast<int>((words + 255) / 256 < 65535 ? (words + 255) / 256 : 65535);
+    pack_codes_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        codes, reinterpret_cast<uint32_t*>(out), rows, K, transpose);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, void* stream) {
+    if (!zeros_bf16 || !out) return ADE_ERR_NULL;
+    if (count == 0) return ADE_OK;
+    const int blocks = static_cast<int>((count + 255) / 256 < 65535 ? (count + 255) / 256 : 65535);
+    pack_zeros_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(zeros_bf16, out, count);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+size_t ade_b200_factored_scratch_bytes(int T, int r) {
+    if (T < 1 || r < 1) return 0;
+    const size_t b = static_cast<size_t>(T) * r * sizeof(__nv_bfloat16);
+    return (b + 255) & ~static_cast<size_t>(255);
+}
+
+int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b, void* out,
+                      void* scratch, size_t scratch_bytes, int T, void* stream) {
+    int rc = check_delta(d);
+    if (rc) return rc;
+    if (!d->vt || !x || !out || !scratch) return ADE_ERR_NULL;
+    if ((y_dense == nullptr) == (w_b == nullptr)) return ADE_ERR_NULL;      // exactly one base term
+    if (T < 1 || T > ADE_B200_MAX_TOKENS || d->M % ade::HU_ROWS) return ADE_ERR_SHAPE;
+    if (!aligned16(d->vt) || !aligned16(x) || !aligned16(out) || !aligned16(scratch) ||
+        (y_dense && !aligned16(y_dense)) || (w_b && !aligned16(w_b)))
+        return ADE_ERR_ALIGN;
+    if (scratch_bytes < ade_b200_factored_scratch_bytes(T, d->r)) return ADE_ERR_SCRATCH;
+    const DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc) return rc;
+    const auto* xb = static_cast<const __nv_bfloat16*>(x);
+    const auto* yb = static_cast<const __nv_bfloat16*>(y_dense);
+    const auto* wb = static_cast<const __nv_bfloat16*>(w_b);
+    auto* ob = static_cast<__nv_bfloat16*>(out);
+    auto* hb = static_cast<__nv_bfloat16*>(scratch);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (T <= 8) return launch_factored<1>(d, xb, yb, wb, ob, hb, T, st);
+    if (T <= 16) return launch_factored<2>(d, xb, yb, wb, ob, hb, T, st);
+    if (T <= 32) return launch_factored<4>(d, xb, yb, wb, ob, hb, T, st);
+    if (T <= 64) return launch_factored<8>(d, xb, yb, wb, ob, hb, T, st);
+    return launch_factored<16>(d, xb, yb, wb, ob, hb, T, st);
+}
+
+int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* dbg_acc, int* status_dev,
+                   void* stream) {
+    int rc = check_delta(d);
+    if (rc) return rc;
+    if (!d->vq || !w_b || !w_out) return ADE_ERR_NULL;
+    if (w_b == w_out) return ADE_ERR_NULL;
+    if (!aligned16(d->vq) || !aligned16(w_b) || !aligned16(w_out) || (dbg_acc && !aligned16(dbg_acc)))
+        return ADE_ERR_ALIGN;
+    const DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc) return rc;
+    ade::ReconParams p;
+    p.uq = d->uq;
+    p.vq = d->vq;
+    p.us = d->us;
+    p.uz = d->uz;
+    p.vs = d->vs;
+    p.vz = d->vz;
+    p.wb = static_cast<const __nv_bfloat16*>(w_b);
+    p.out = static_cast<__nv_bfloat16*>(w_out);
+    p.dbg = dbg_acc;
+    p.status = status_dev;
+    p.M = d->M;
+    p.N = d->N;
+    p.r = d->r;
+    const int ng = d->r / ADE_B200_GROUP;
+    const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
+    const int grid = ntiles < di->sms ? ntiles : di->sms;
+    if (dbg_acc)
+        ade::recon_kernel<true><<<grid, ade::RC_THREADS, ade::recon_smem_bytes(ng), static_cast<cudaStream_t>(stream)>>>(p);
+    else
+        ade::recon_kernel<false><<<grid, ade::RC_THREADS, ade::recon_smem_bytes(ng), static_cast<cudaStream_t>(stream)>>>(p);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+"""Host side of the B200 delta-application kernels.
+
+Mirrors the public surface of the reference's ``src/kernels.py`` -- ``pack_int4``,
+``decode_forward_packed``, ``recon_int4``, ``decode_kernel_status``, ``recon_kernel_status``
+(the five names ``src/serving.py:35`` imports) -- on top of the C ABI of include/ade_b200.h.
+Differences a caller sees: 16-bit tensors are bfloat16 (the reference kernels are float16),
+the stored form has its own layout (see ``pack_int4``), nothing is compiled at run time and
+there is no autotuning pass or PyTorch fallback: a missing library or an unsupported shape
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+GROUP = 128
+_NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)      # nibble i of a 32-bit word holds code _NIBBLE_ORDER[i]
+STORED_KEYS = ("uq", "vq", "vt", "us", "uz", "vs", "vz")
+
+
+# ---------------------------------------------------------------------------- status
+def _status(device) -> tuple[bool, str]:
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        return False, "no CUDA device"
+    major, minor = torch.cuda.get_device_capability(dev)
+    if major != 10:
+        return False, f"compute capability {major}.{minor} is not 10.x (the kernels are built for sm_100a only)"
+    try:
+        lib = _lib.load()
+    except _lib.AdeKernelError as e:
+        return False, str(e)
+    with torch.cuda.device(dev):
+        rc = lib.ade_b200_device_status()
+    if rc != 0:
+        return False, _lib.ERRORS.get(rc, str(rc))
+    return True, f"sm_{major}{minor}a"
+
+
+def recon_kernel_status(device="cuda"):
+    """Whether the tcgen05 reconstruction kernel can run on `device` (src/kernels.py:86-104)."""
+    return _status(device)
+
+
+def decode_kernel_status(device="cuda"):
+    """Whether the factored-application kernels can run on `device` (src/kernels.py:107-124)."""
+    return _status(device)
+
+
+# ---------------------------------------------------------------------------- stored form
+def pack_nibbles(codes: torch.Tensor) -> torch.Tensor:
+    """(..., K) uint8 codes in 0..15 -> (..., K/2) uint8, eight codes per 32-bit word.
+
+    Replaces ``_pack_nibbles`` (src/kernels.py:145-161).  Nibble i of each little-endian word
+    holds code (0, 2, 4, 6, 1, 3, 5, 7)[i] of its 8 codes, so ``(w >> 4j) & 0x000F000F`` is the
+    adjacent pair (c_2j, c_2j+1) in the two halves of a register.
+    """
+    K = codes.shape[-1]
+    if K % 8:
+        raise ValueError(f"pack_nibbles: last dimension {K} is not a multiple of 8")
+    c = codes.to(torch.uint8).reshape(*codes.shape[:-1], K // 8, 8)[..., list(_NIBBLE_ORDER)]
+    return (c[..., 0::2] | (c[..., 1::2] << 4)).reshape(*codes.shape[:-1], K // 2).contiguous()
+
+
+def unpack_nibbles(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``pack_nibbles`` (used by tests and tools, not by the kernels)."""
+    K2 = packed.shape[-1]
+    b = packed.reshape(*packed.shape[:-1], K2 // 4, 4)
+    nib = torch.stack([b & 15, b >> 4], -1).reshape(*packed.shape[:-1], K2 // 4, 8)   # nibble order
+    out = torch.empty_like(nib)
+    out[..., list(_NIBBLE_ORDER)] = nib
+    return out.reshape(*packed.shape[:-1], K2 * 2)
+
+
+def pack_int4(packed: dict, group_size: int = GROUP, device=None) -> dict:
+    """Stored form of one compressed module, read by both kernels (replaces src/kernels.py:164-188).
+
+    Parameters:
+        packed: dict with U_codes, U_scale, U_zero, Vt_codes, Vt_scale, Vt_zero as
+            ``quantization.compress_module`` writes them (src/quantization.py:276-285).
+        group_size: G; only 128 is supported.
+        device: where to build the stored form (default: where the packed tensors are).
+
+    Returns:
+        dict with ``uq`` (M, r/2), ``vq`` (N, r/2), ``vt`` (r, N/2) uint8 nibble-packed codes,
+        ``us`` (M, ng) / ``vs`` (ng, N) bfloat16 scales, ``uz`` (M, ng) / ``vz`` (ng, N) uint8
+        zero-points, and the ints ``M``, ``N``, ``r``.  Unlike the reference there are no FP32
+        side tables: the kernels subtract the zero-points from the codes before contracting.
+    """
+    if group_size != GROUP:
+        raise ValueError("the kernels are specialised for group size 128")
+    dev = torch.device(device) if device is not None else packed["U_codes"].device
+    uc = packed["U_codes"].to(dev, torch.uint8)
+    vc = packed["Vt_codes"].to(dev, torch.uint8)
+    M, r = uc.shape
+    r2, N = vc.shape
+    if r != r2 or r % GROUP:
+        raise ValueError(f"pack_int4: rank {r} / {r2} must match and be a multiple of {GROUP}")
+    if N % 8:
+        raise ValueError(f"pack_int4: d_i = {N} must be a multiple of 8")
+    out = {
+        "uq": pack_nibbles(uc),
+        "vq": pack_nibbles(vc.t().contiguous()),
+        "vt": pack_nibbles(vc),
+        "us": packed["U_scale"].to(dev, torch.bfloat16).contiguous(),
+        "uz": packed["U_zero"].to(dev).to(torch.float32).to(torch.uint8).contiguous(),
+        "vs": packed["Vt_scale"].to(dev, torch.bfloat16).contiguous(),
+        "vz": packed["Vt_zero"].to(dev).to(torch.float32).to(torch.uint8).contiguous(),
+        "M": M, "N": N, "r": r,
+    }
+    return out
+
+
+def _cdelta(p4: dict):
+    """ctypes view of a stored form, cached in the dict (rebuilt if the tensors moved)."""
+    key = tuple(p4[k].data_ptr() for k in STORED_KEYS)
+    c = p4.get("_cdelta")
+    if c is None or c[0] != key:
+        for k in STORED_KEYS:
+            t = p4[k]
+            if not (t.is_cuda and t.is_contiguous()):
+                raise ValueError(f"stored form tensor {k} must be a contiguous CUDA tensor")
+        d = _lib.AdeDelta(*key, int(p4["M"]), int(p4["N"]), int(p4["r"]))
+        c = p4["_cdelta"] = (key, d)
+    return c[1]
+
+
+# ---------------------------------------------------------------------------- launches
+_scratch: dict = {}
+
+
+def _scratch_for(dev: torch.device, stream_ptr: int, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch per (device, stream): h = V^T x lives here between the two launches."""
+    key = (dev.index, stream_ptr)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = _scratch[key] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+    return buf
+
+
+def _check_x(x: torch.Tensor, N: int, what: str):
+    if x.dtype != torch.bfloat16 or not x.is_cuda or not x.is_contiguous() or x.dim() != 2 or x.shape[1] != N:
+        raise ValueError(f"{what} must be a contiguous CUDA bfloat16 tensor of shape (T, {N}); got "
+                         f"{tuple(x.shape)} {x.dtype} on {x.device}")
+
+
+def factored_forward(x: torch.Tensor, p4: dict, weight: torch.Tensor | None = None,
+                     y_dense: torch.Tensor | None = None) -> torch.Tensor:
+    """out = base + U^(V^T x) for T <= 128 tokens; base = x W_b^T computed in-kernel when `weight`
+    is given, else the supplied `y_dense`.  One call of ``ade_b200_factored``."""
+    lib = _lib.load()
+    M, N, r = int(p4["M"]), int(p4["N"]), int(p4["r"])
+    _check_x(x, N, "x")
+    T = x.shape[0]
+    if (weight is None) == (y_dense is None):
+        raise ValueError("give exactly one of weight (fused base GEMM) or y_dense")
+    if weight is not None and not (weight.dtype == torch.bfloat16 and weight.is_contiguous()
+                                   and tuple(weight.shape) == (M, N) and weight.device == x.device):
+        raise ValueError("weight must be a contiguous bfloat16 (d_o, d_i) tensor on x's device")
+    if y_dense is not None:
+        _check_x(y_dense, M, "y_dense")
+        if y_dense.shape[0] != T:
+            raise ValueError("y_dense and x disagree on T")
+    out = torch.empty((T, M), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        nbytes = lib.ade_b200_factored_scratch_bytes(T, r)
+        scratch = _scratch_for(x.device, stream, nbytes)
+        rc = lib.ade_b200_factored(
+            ctypes.byref(_cdelta(p4)), x.data_ptr(),
+            None if y_dense is None else y_dense.data_ptr(),
+            None if weight is None else weight.data_ptr(),
+            out.data_ptr(), scratch.data_ptr(), scratch.numel(), T, stream)
+    _lib.check(rc, "ade_b200_factored")
+    return out
+
+
+def decode_forward_packed(x, y_dense, p4, group_size=GROUP, split_k=False):
+    """Factored application y_dense + U^ (V^^T x) (same signature as src/kernels.py:1182-1200).
+
+    x (T, d_i) and y_dense (T, d_o) are contiguous bfloat16 CUDA tensors; returns a fresh (T, d_o)
+    bfloat16 tensor.  `split_k` is accepted for compatibility and ignored: the contraction is
+    split inside a CTA and reduced in a fixed order, so there is no atomic variant to choose.
+    """
+    if group_size != GROUP:
+        raise ValueError("the kernels are specialised for group size 128")
+    return factored_forward(x, p4, y_dense=y_dense)
+
+
+def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None):
+    """W_b + U^ V^^T of one module in bfloat16 (same role as src/kernels.py:431-444).
+
+    `dbg_acc`: optional int32 (ng, d_o, d_i) CUDA tensor that receives every group's INT32
+    accumulator; `status`: optional int32 CUDA scalar tensor for the kernel's timeout code.
+    """
+    if group_size != GROUP:
+        raise ValueError("the kernels are specialised for group size 128")
+    lib = _lib.load()
+    M, N, r = int(p4["M"]), int(p4["N"]), int(p4["r"])
+    if not (base.dtype == torch.bfloat16 and base.is_cuda and tuple(base.shape) == (M, N)):
+        raise ValueError(f"base must be a CUDA bfloat16 ({M}, {N}) tensor")
+    base = base.contiguous()
+    out = torch.empty_like(base)
+    if dbg_acc is not None and not (dbg_acc.dtype == torch.int32 and dbg_acc.is_contiguous()
+                                    and tuple(dbg_acc.shape) == (r // GROUP, M, N)):
+        raise ValueError("dbg_acc must be a contiguous int32 (ng, d_o, d_i) tensor")
+    with torch.cuda.device(base.device):
+        rc = lib.ade_b200_recon(
+            ctypes.byref(_cdelta(p4)), base.data_ptr(), out.data_ptr(),
+            None if dbg_acc is None else dbg_acc.data_ptr(),
+            None if status is None else status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "ade_b200_recon")
+    return out

@@ -1,0 +1,136 @@
+/*
+ * ade_b200.h -- C ABI of the B200 (sm_100a) delta-application kernels.
+ *
+ * The library replaces the native half of the reference's src/kernels.py: the two CUDA
+ * extensions that file builds at run time (ade_recon_int4, src/kernels.py:383-397, and
+ * run_a / run_b / run_ab, src/kernels.py:935-954).  Every entry point takes plain device
+ * pointers and sizes, launches on the stream it is given, allocates nothing and returns
+ * an int status (0 = ok, negative = rejected before any launch).  Nothing throws across
+ * this boundary.
+ *
+ * All 16-bit floating-point buffers are bfloat16.  "Packed delta" below is the device
+ * stored form described at ade_delta_t; it is produced from the six tensors that the
+ * reference's src/quantization.py:276-285 writes by ade_b200_pack_* (or by the Python
+ * helper ade_b200.kernels.pack_int4, which replaces src/kernels.py:164-188).
+ */
+#ifndef ADE_B200_H
+#define ADE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADE_B200_GROUP 128          /* ranks per quantization group (G); the only supported value */
+#define ADE_B200_MAX_RANK 4096
+#define ADE_B200_MAX_TOKENS 128     /* largest T of the factored path (src/serving.py:105) */
+
+/* return codes */
+#define ADE_OK 0
+#define ADE_ERR_NULL (-1)           /* a required pointer is NULL */
+#define ADE_ERR_SHAPE (-2)          /* a dimension is out of the supported set */
+#define ADE_ERR_ALIGN (-3)          /* a pointer is not 16-byte aligned */
+#define ADE_ERR_SCRATCH (-4)        /* scratch buffer too small */
+#define ADE_ERR_CUDA (-5)           /* a CUDA runtime call failed (see ade_b200_last_cuda_error) */
+#define ADE_ERR_DEVICE (-6)         /* current device is not compute capability 10.x */
+
+/* device-side status word values written by the reconstruction kernel (0 = clean run) */
+#define ADE_DEV_OK 0
+#define ADE_DEV_TIMEOUT_FULL 1      /* MMA warp gave up waiting for an operand stage */
+#define ADE_DEV_TIMEOUT_EMPTY 2     /* unpack warps gave up waiting for a free operand stage */
+#define ADE_DEV_TIMEOUT_TMEM_FULL 3 /* epilogue gave up waiting for an accumulator */
+#define ADE_DEV_TIMEOUT_TMEM_EMPTY 4/* MMA warp gave up waiting for a free accumulator */
+
+/*
+ * Device stored form of one compressed module (all pointers are device memory, 16-byte
+ * aligned).  M = d_o, N = d_i, r = rank (multiple of 128), ng = r / 128.
+ *
+ *   uq  uint8 [M][r/2]   codes of U^, two per byte, packed along the rank axis.  Inside
+ *                        each group of 8 consecutive codes c0..c7 (one 32-bit word) nibble i
+ *                        (bits 4i..4i+3) holds c0,c2,c4,c6,c1,c3,c5,c7 for i = 0..7, so that
+ *                        (w >> 4j) & 0x000F000F yields the adjacent pair (c2j, c2j+1).
+ *   vq  uint8 [N][r/2]   codes of V^ (V^T transposed), same packing along the rank axis;
+ *                        read by the reconstruction kernel.
+ *   vt  uint8 [r][N/2]   codes of V^T in their natural orientation, same packing along the
+ *                        d_i axis; read by the factored kernel.
+ *   us  bf16  [M][ng]    per-group scales of U^           (U_scale, src/quantization.py:164)
+ *   uz  uint8 [M][ng]    per-group zero-points of U^, 0..15 (U_zero, src/quantization.py:165)
+ *   vs  bf16  [ng][N]    per-group scales of V^T           (Vt_scale, src/quantization.py:198)
+ *   vz  uint8 [ng][N]    per-group zero-points of V^T      (Vt_zero, src/quantization.py:199)
+ *
+ * This replaces the reference's stored form {uq, vq, R, C} (src/kernels.py:164-188): the
+ * FP32 side tables R / C are not stored; the zero-points are subtracted from the codes
+ * before the integer contraction, exactly as src/quantization.py:305-308 does.
+ */
+typedef struct ade_delta {
+    const uint8_t* uq;
+    const uint8_t* vq;
+    const uint8_t* vt;
+    const uint16_t* us;
+    const uint8_t* uz;
+    const uint16_t* vs;
+    const uint8_t* vz;
+    int M, N, r;
+} ade_delta_t;
+
+/* Library / device checks.  Replaces decode_kernel_status / recon_kernel_status
+ * (src/kernels.py:86-124): returns ADE_OK when the current CUDA device can run the
+ * kernels (compute capability 10.x), ADE_ERR_DEVICE / ADE_ERR_CUDA otherwise. */
+int ade_b200_device_status(void);
+int ade_b200_version(void);
+/* cudaError_t of the most recent failing runtime call on this thread, 0 if none */
+int ade_b200_last_cuda_error(void);
+
+/*
+ * Stored-form packing on the device (replaces the CPU packing of src/kernels.py:145-188).
+ * codes: uint8 [rows][K], one 4-bit code per byte (src/quantization.py:162-163,196-197).
+ * out:   uint8 [rows][K/2] in the nibble order documented at ade_delta_t.  K % 8 == 0.
+ * With transpose != 0 the input is read as [K][rows] (used to build vq from Vt_codes).
+ */
+int ade_b200_pack_codes(const uint8_t* codes, uint8_t* out, int rows, int K, int transpose, void* stream);
+/* zero-points: bfloat16 holding an integer 0..15 -> uint8 (count elements) */
+int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, void* stream);
+
+/*
+ * Factored application, T <= 128 tokens (replaces run_ab, src/kernels.py:946-954, and the
+ * F.linear that precedes it in src/serving.py:106):
+ *
+ *     out[t][m] = base_term[t][m] + sum_k U^[m][k] * ( sum_n V^T[k][n] * x[t][n] )
+ *
+ * base_term is y_dense[t][m] when y_dense != NULL (the reference's calling convention,
+ * src/kernels.py:1182-1200), or sum_n w_b[m][n] x[t][n] computed inside the same kernel
+ * when w_b != NULL (exactly one of the two must be given).
+ *   x bf16 [T][N], y_dense bf16 [T][M], w_b bf16 [M][N], out bf16 [T][M].
+ *   scratch: device buffer of at least ade_b200_factored_scratch_bytes(T, r) bytes, holds
+ *   h = V^T x between the two launches; contents need no initialisation.
+ * Requirements: 1 <= T <= 128, M % 32 == 0, N % 128 == 0, r % 128 == 0.
+ * Two kernels are launched on `stream`; the call does not synchronise.
+ */
+size_t ade_b200_factored_scratch_bytes(int T, int r);
+int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b,
+                      void* out, void* scratch, size_t scratch_bytes, int T, void* stream);
+
+/*
+ * Reconstructed application (replaces ade_recon_int4, src/kernels.py:383-397):
+ *
+ *     w_out[m][n] = bf16( float(w_b[m][n]) + sum_g (us[m][g] * vs[g][n]) * float(P_g[m][n]) )
+ *     P_g[m][n]   = sum_{k in group g} (Ucode[m][k] - uz[m][g]) * (Vcode[k][n] - vz[g][n])   (INT32)
+ *
+ * the arithmetic of src/quantization.py:303-315 followed by the add of src/serving.py:92,
+ * in the same order and with the same float32 roundings.  P_g is contracted with
+ * tcgen05 kind::i8 MMAs into tensor memory.
+ *   w_b, w_out bf16 [M][N] (may not alias).  Requirements: N % 128 == 0, r % 128 == 0, M >= 1.
+ *   dbg_acc: optional int32 [ng][M][N]; when non-NULL every P_g is also written there.
+ *   status_dev: optional device int; set to a non-zero ADE_DEV_* code if a bounded wait
+ *   inside the kernel expired (the kernel then still terminates; w_out is undefined).
+ *   It is not cleared by the call.
+ */
+int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
+                   int32_t* dbg_acc, int* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADE_B200_H */
