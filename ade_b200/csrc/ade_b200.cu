@@ -23,11 +23,15 @@ inline bool cuda_ok(cudaError_t e) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kMaxDevices = 64;
+constexpr int kMaxRowsCap = 320;    // rows of one CTA's slice that fit the shared-memory y buffer (T = 128)
 struct DeviceInfo {
     int ready = 0;      // 1 = usable, -1 = wrong architecture
     int sms = 0;
 };
 DeviceInfo g_dev[kMaxDevices];
+
+template <int NT>
+bool optin_factored();
 
 // per-device set-up: architecture check, SM count, dynamic shared-memory opt-in
 int device_info(const DeviceInfo** out) {
@@ -45,6 +49,9 @@ int device_info(const DeviceInfo** out) {
             const int smem = static_cast<int>(ade::recon_smem_bytes(ADE_B200_MAX_RANK / 128));
             if (!cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                return ADE_ERR_CUDA;
+            if (!optin_factored<1>() || !optin_factored<2>() || !optin_factored<4>() || !optin_factored<8>() ||
+                !optin_factored<16>())
                 return ADE_ERR_CUDA;
             d.sms = sms;
             d.ready = 1;
@@ -89,19 +96,24 @@ __global__ void pack_zeros_kernel(const uint16_t* __restrict__ z, uint8_t* __res
         out[i] = static_cast<uint8_t>(static_cast<int>(ade::bf16_bits_to_f32(z[i])));
 }
 
+template <int NT, bool FUSE>
+int launch_factored_one(const ade::FactoredParams& p, int grid, cudaStream_t st) {
+    const size_t smem = ade::factored_smem_bytes(NT, FUSE ? p.rows_cap : 0);
+    ade::factored_kernel<NT, FUSE><<<grid, ade::FA_THREADS, smem, st>>>(p);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
 template <int NT>
-int launch_factored(const ade_delta_t* d, const __nv_bfloat16* x, const __nv_bfloat16* y_dense,
-                    const __nv_bfloat16* w_b, __nv_bfloat16* out, __nv_bfloat16* h, int T, cudaStream_t st) {
-    ade::xv_kernel<NT><<<d->r / 16, ade::XV_THREADS, 0, st>>>(d->vt, d->vs, d->vz, x, h, T, d->N, d->r);
-    if (!cuda_ok(cudaGetLastError())) return ADE_ERR_CUDA;
-    if (w_b)
-        ade::hu_kernel<NT, true><<<d->M / ade::HU_ROWS, ade::HU_THREADS, 0, st>>>(w_b, x, nullptr, d->uq, d->us, d->uz,
-                                                                                 h, out, T, d->M, d->N, d->r);
-    else
-        ade::hu_kernel<NT, false><<<d->M / ade::HU_ROWS, ade::HU_THREADS, 0, st>>>(nullptr, x, y_dense, d->uq, d->us,
-                                                                                  d->uz, h, out, T, d->M, d->N, d->r);
-    if (!cuda_ok(cudaGetLastError())) return ADE_ERR_CUDA;
-    return ADE_OK;
+int launch_factored(const ade::FactoredParams& p, int grid, cudaStream_t st) {
+    return p.w_b ? launch_factored_one<NT, true>(p, grid, st) : launch_factored_one<NT, false>(p, grid, st);
+}
+
+template <int NT>
+bool optin_factored() {
+    const int smem = static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap));
+    return cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) &&
+           cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(ade::factored_smem_bytes(NT, 0))));
 }
 
 }  // namespace
@@ -139,7 +151,12 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
 size_t ade_b200_factored_scratch_bytes(int T, int r) {
     if (T < 1 || r < 1) return 0;
     const size_t b = static_cast<size_t>(T) * r * sizeof(__nv_bfloat16);
-    return (b + 255) & ~static_cast<size_t>(255);
+    return ((b + 255) & ~static_cast<size_t>(255)) + 256;          // h, then the three sync words
+}
+
+size_t ade_b200_factored_sync_offset(int T, int r) {
+    const size_t n = ade_b200_factored_scratch_bytes(T, r);
+    return n ? n - 256 : 0;
 }
 
 int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b, void* out,
@@ -148,7 +165,7 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     if (rc) return rc;
     if (!d->vt || !x || !out || !scratch) return ADE_ERR_NULL;
     if ((y_dense == nullptr) == (w_b == nullptr)) return ADE_ERR_NULL;      // exactly one base term
-    if (T < 1 || T > ADE_B200_MAX_TOKENS || d->M % ade::HU_ROWS) return ADE_ERR_SHAPE;
+    if (T < 1 || T > ADE_B200_MAX_TOKENS) return ADE_ERR_SHAPE;
     if (!aligned16(d->vt) || !aligned16(x) || !aligned16(out) || !aligned16(scratch) ||
         (y_dense && !aligned16(y_dense)) || (w_b && !aligned16(w_b)))
         return ADE_ERR_ALIGN;
@@ -156,17 +173,32 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     const DeviceInfo* di = nullptr;
     rc = device_info(&di);
     if (rc) return rc;
-    const auto* xb = static_cast<const __nv_bfloat16*>(x);
-    const auto* yb = static_cast<const __nv_bfloat16*>(y_dense);
-    const auto* wb = static_cast<const __nv_bfloat16*>(w_b);
-    auto* ob = static_cast<__nv_bfloat16*>(out);
-    auto* hb = static_cast<__nv_bfloat16*>(scratch);
+    ade::FactoredParams p;
+    p.w_b = static_cast<const __nv_bfloat16*>(w_b);
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.y_dense = static_cast<const __nv_bfloat16*>(y_dense);
+    p.uq = d->uq;
+    p.vt = d->vt;
+    p.us = d->us;
+    p.uz = d->uz;
+    p.vs = d->vs;
+    p.vz = d->vz;
+    p.h = static_cast<__nv_bfloat16*>(scratch);
+    p.sync = reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + ade_b200_factored_sync_offset(T, d->r));
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.T = T;
+    p.M = d->M;
+    p.N = d->N;
+    p.r = d->r;
+    const int grid = di->sms;                                   // one persistent CTA per SM, all co-resident
+    p.rows_cap = (((d->M + grid - 1) / grid) + 31) / 32 * 32;
+    if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (T <= 8) return launch_factored<1>(d, xb, yb, wb, ob, hb, T, st);
-    if (T <= 16) return launch_factored<2>(d, xb, yb, wb, ob, hb, T, st);
-    if (T <= 32) return launch_factored<4>(d, xb, yb, wb, ob, hb, T, st);
-    if (T <= 64) return launch_factored<8>(d, xb, yb, wb, ob, hb, T, st);
-    return launch_factored<16>(d, xb, yb, wb, ob, hb, T, st);
+    if (T <= 8) return launch_factored<1>(p, grid, st);
+    if (T <= 16) return launch_factored<2>(p, grid, st);
+    if (T <= 32) return launch_factored<4>(p, grid, st);
+    if (T <= 64) return launch_factored<8>(p, grid, st);
+    return launch_factored<16>(p, grid, st);
 }
 
 int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* dbg_acc, int* status_dev,

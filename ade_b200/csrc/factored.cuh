@@ -1,32 +1,60 @@
-// Factored application  out = base_term + U^ (V^T x)  for T <= 128 tokens.
+// Factored application  out = base_term + U^ (V^T x)  for T <= 128 tokens, one launch.
 //
-// Replaces the reference's decode kernels A and B (src/kernels.py:486-886).  Two launches:
+// Replaces the reference's decode kernels A and B and the cuBLAS call in front of them
+// (src/kernels.py:486-886, src/serving.py:106).  One persistent grid (one CTA per SM) does, per CTA:
 //
-//   xv_kernel : h[t][k]   = sum_n bf16((Vcode[k][n] - vz[g][n]) * vs[g][n]) * x[t][n]      (fp32 accumulate)
-//   hu_kernel : out[t][m] = base[t][m] + sum_g us[m][g] * sum_{k in g} (Ucode[m][k] - uz[m][g]) * h[t][k]
-//               with base = y_dense (given) or  sum_n w_b[m][n] x[t][n]  streamed in the same kernel.
+//   phase A  (a few CTAs)  h[t][k] = sum_n bf16((Vcode[k][n] - vz[g][n]) * vs[g][n]) * x[t][n] for 16 ranks k,
+//                          written to global scratch as bf16, then one release-increment of a counter;
+//   phase W  (all CTAs)    y[t][m] = sum_n w_b[m][n] x[t][n] for this CTA's contiguous slice of rows m,
+//                          kept in shared memory (skipped when the caller supplies y_dense);
+//   wait                   until the counter shows that every h unit has been written (bounded spin);
+//   phase U  (all CTAs)    out[t][m] = y[t][m] + sum_g us[m][g] * sum_{k in g} (Ucode[m][k] - uz[m][g]) * h[t][k].
 //
-// Both are weight-streaming skinny GEMMs: the weights (bf16 rows of W_b, or 4-bit codes) are
-// the 16-row operand of a warp MMA and come straight from global memory with 128-bit loads;
-// the activations (x or h, a few KB that live in L1/L2) are the 8-column operand.  The
-// contraction axis is split over the warps of a CTA and reduced through shared memory in a
-// fixed order, so results do not depend on scheduling (no atomics).
+// Phase A is 3 % of the bytes and finishes long before phase W does, so the grid-wide dependency
+// h -> phase U costs no idle time.  Rows are split evenly over the CTAs (to within one row), so
+// every SM streams the same number of bytes of W_b.
 //
-// Fragment bookkeeping (mma.m16n8k16, lane = 4*gid + tig): a thread's 16-byte load covers
-// 8 bf16 (or 32 codes) of one weight row; consecutive 4-element slices of it are used as the
-// thread's k-slots {2tig, 2tig+1, 2tig+8, 2tig+9} of consecutive MMAs, and the activation
-// fragment is read from the same 4 columns, so the products line up without any shuffle.
+// All three phases are weight-streaming skinny GEMMs: the weights (bf16 rows of W_b, or 4-bit codes)
+// are the 16-row operand of a warp MMA and come straight from global memory with 128-bit loads, a
+// few blocks ahead of their use; the activations (x or h, L1/L2 resident) are the 8-column operand.
+// The contraction axis is split over the 8 warps of a CTA and reduced through shared memory in a
+// fixed order, so results do not depend on scheduling (no floating-point atomics).
+//
+// Fragment bookkeeping (mma.m16n8k16, lane = 4*gid + tig): a thread's 16-byte load covers 8 bf16 (or
+// 32 codes) of one weight row; consecutive 4-element slices of it are used as the thread's k-slots
+// {2tig, 2tig+1, 2tig+8, 2tig+9} of consecutive MMAs, and the activation fragment is read from the
+// same 4 columns, so the products line up without any shuffle.
 #pragma once
 #include "ptx.cuh"
 
 namespace ade {
 
-constexpr int XV_WARPS = 16;
-constexpr int XV_THREADS = XV_WARPS * 32;
-constexpr int HU_WARPS = 8;
-constexpr int HU_THREADS = HU_WARPS * 32;
-constexpr int HU_ROWS = 32;          // output rows per CTA (two m16 tiles per warp)
-constexpr uint32_t kBf2_128 = 0x43004300u;   // bf16x2 (128, 128)
+constexpr int FA_WARPS = 8;
+constexpr int FA_THREADS = FA_WARPS * 32;
+constexpr int FA_ROWS = 32;                    // output rows per pass (two m16 tiles per warp)
+constexpr uint32_t kBf2_128 = 0x43004300u;     // bf16x2 (128, 128)
+constexpr long long FA_SPIN_LIMIT = 2000000000LL;   // clock cycles (about one second)
+
+struct FactoredParams {
+    const __nv_bfloat16* w_b;      // [M][N] or nullptr
+    const __nv_bfloat16* x;        // [T][N]
+    const __nv_bfloat16* y_dense;  // [T][M] or nullptr
+    const uint8_t* uq;             // [M][r/2]
+    const uint8_t* vt;             // [r][N/2]
+    const uint16_t* us;            // [M][ng]
+    const uint8_t* uz;             // [M][ng]
+    const uint16_t* vs;            // [ng][N]
+    const uint8_t* vz;             // [ng][N]
+    __nv_bfloat16* h;              // scratch [T][r]
+    unsigned int* sync;            // scratch: [0] units arrived, [1] CTAs done, [2] status (0 = ok)
+    __nv_bfloat16* out;            // [T][M]
+    int T, M, N, r;
+    int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
+};
+
+__host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap) {
+    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + static_cast<size_t>(rows_cap) * (8 * NT + 1)) * sizeof(float);
+}
 
 // one packed word (8 codes) -> 4 bf16x2 registers holding 128 + code, codes in natural order
 __device__ __forceinline__ void unpack8_bf16(uint32_t w, uint32_t (&e)[4]) {
@@ -36,230 +64,11 @@ __device__ __forceinline__ void unpack8_bf16(uint32_t w, uint32_t (&e)[4]) {
     e[3] = ((w >> 12) & 0x000F000Fu) | kBf2_128;
 }
 
-// ---------------------------------------------------------------------------------------
-// h = V^T x.  grid = r / 16 CTAs (16 ranks each), XV_THREADS threads; the d_i axis is split
-// over the warps in chunks of 128 columns.
-// ---------------------------------------------------------------------------------------
-template <int NT>
-__global__ void __launch_bounds__(XV_THREADS)
-xv_kernel(const uint8_t* __restrict__ vt, const uint16_t* __restrict__ vs, const uint8_t* __restrict__ vz,
-          const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ h, int T, int N, int r) {
-    __shared__ float red[XV_WARPS][16][33];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-    const int k0 = blockIdx.x * 16;
-    const int g = k0 >> 7;
-    const size_t rowb = static_cast<size_t>(N >> 1);
-    const uint8_t* row0 = vt + static_cast<size_t>(k0 + gid) * rowb;
-    const uint8_t* row1 = row0 + 8 * rowb;
-
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-
-    const int nchunks = N >> 7;
-    for (int c = warp; c < nchunks; c += XV_WARPS) {
-        const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
-        const uint4 q0 = ldg16_stream(row0 + (nb >> 1));
-        const uint4 q1 = ldg16_stream(row1 + (nb >> 1));
-        const uint16_t* sp = vs + static_cast<size_t>(g) * N + nb;
-        const uint8_t* zp = vz + static_cast<size_t>(g) * N + nb;
-        const uint4 s0 = ldg16(sp), s1 = ldg16(sp + 8), s2 = ldg16(sp + 16), s3 = ldg16(sp + 24);
-        const uint4 z0 = ldg16(zp), z1 = ldg16(zp + 16);
-        const uint32_t cw0[4] = {q0.x, q0.y, q0.z, q0.w};
-        const uint32_t cw1[4] = {q1.x, q1.y, q1.z, q1.w};
-        const uint32_t sw[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w,
-                                 s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
-        const uint32_t zw[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-#pragma unroll
-        for (int wi = 0; wi < 4; ++wi) {                  // 8 columns per packed word
-            uint32_t e0[4], e1[4], a0[4], a1[4];
-            unpack8_bf16(cw0[wi], e0);
-            unpack8_bf16(cw1[wi], e1);
-            const uint32_t zz[4] = {__byte_perm(zw[2 * wi], 0x43434343u, 0x4140),
-                                    __byte_perm(zw[2 * wi], 0x43434343u, 0x4342),
-                                    __byte_perm(zw[2 * wi + 1], 0x43434343u, 0x4140),
-                                    __byte_perm(zw[2 * wi + 1], 0x43434343u, 0x4342)};
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {                 // (code - zero) is exact; one rounding in the product
-                a0[p] = bf2_mul(bf2_sub(e0[p], zz[p]), sw[4 * wi + p]);
-                a1[p] = bf2_mul(bf2_sub(e1[p], zz[p]), sw[4 * wi + p]);
-            }
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int tok = nt * 8 + gid;
-                uint4 xq = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < T) xq = ldg16(x + static_cast<size_t>(tok) * N + nb + 8 * wi);
-                mma_bf16(acc[nt], a0[0], a1[0], a0[1], a1[1], xq.x, xq.y);
-                mma_bf16(acc[nt], a0[2], a1[2], a0[3], a1[3], xq.z, xq.w);
-            }
-        }
-    }
-
-    // fixed-order reduction over the warps, 32 tokens (4 token tiles) at a time
-#pragma unroll
-    for (int b = 0; b < (NT + 3) / 4; ++b) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int nt = b * 4 + j;
-            if (nt < NT) {
-                red[warp][gid][j * 8 + 2 * tig] = acc[nt][0];
-                red[warp][gid][j * 8 + 2 * tig + 1] = acc[nt][1];
-                red[warp][gid + 8][j * 8 + 2 * tig] = acc[nt][2];
-                red[warp][gid + 8][j * 8 + 2 * tig + 1] = acc[nt][3];
-            }
-        }
-        __syncthreads();
-        {
-            const int rank = threadIdx.x & 15, tok = threadIdx.x >> 4;      // 16 x 32 = XV_THREADS
-            const int t = b * 32 + tok;
-            if (tok < 8 * (NT - 4 * b) && t < T) {
-                float s = 0.f;
-#pragma unroll
-                for (int w = 0; w < XV_WARPS; ++w) s += red[w][rank][tok];
-                h[static_cast<size_t>(t) * r + k0 + rank] = __float2bfloat16_rn(s);
-            }
-        }
-        __syncthreads();
-    }
-}
-
-// ---------------------------------------------------------------------------------------
-// out = base + U^ h.  grid = M / 32 CTAs, HU_THREADS threads.
-// ---------------------------------------------------------------------------------------
-template <int NT, bool FUSE_WB>
-__global__ void __launch_bounds__(HU_THREADS)
-hu_kernel(const __nv_bfloat16* __restrict__ w_b, const __nv_bfloat16* __restrict__ x,
-          const __nv_bfloat16* __restrict__ y_dense, const uint8_t* __restrict__ uq,
-          const uint16_t* __restrict__ us, const uint8_t* __restrict__ uz,
-          const __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ out, int T, int M, int N, int r) {
-    __shared__ float red[HU_WARPS][32][33];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-    const int m0 = blockIdx.x * HU_ROWS;
-
-    float acc[2][NT][4];
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
-
-    if (FUSE_WB) {
-        // W_b x: contraction over d_i in blocks of 64 columns, block b -> warp b % HU_WARPS
-        const int nblk = N >> 6;
-        const __nv_bfloat16* wrow[2][2];
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-            wrow[mt][0] = w_b + static_cast<size_t>(m0 + mt * 16 + gid) * N + tig * 8;
-            wrow[mt][1] = wrow[mt][0] + static_cast<size_t>(8) * N;
-        }
-        uint4 cur[2][2][2], nxt[2][2][2];
-        if (warp < nblk) {
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int hr = 0; hr < 2; ++hr)
-#pragma unroll
-                    for (int s = 0; s < 2; ++s) cur[mt][hr][s] = ldg16_stream(wrow[mt][hr] + warp * 64 + s * 32);
-        }
-        for (int b = warp; b < nblk; b += HU_WARPS) {
-            const int bn = b + HU_WARPS;
-            if (bn < nblk) {
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int hr = 0; hr < 2; ++hr)
-#pragma unroll
-                        for (int s = 0; s < 2; ++s) nxt[mt][hr][s] = ldg16_stream(wrow[mt][hr] + bn * 64 + s * 32);
-            }
-            const int kb = b * 64 + tig * 8;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int tok = nt * 8 + gid;
-#pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    uint4 xq = make_uint4(0u, 0u, 0u, 0u);
-                    if (tok < T) xq = ldg16(x + static_cast<size_t>(tok) * N + kb + s * 32);
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        mma_bf16(acc[mt][nt], cur[mt][0][s].x, cur[mt][1][s].x, cur[mt][0][s].y, cur[mt][1][s].y,
-                                 xq.x, xq.y);
-                        mma_bf16(acc[mt][nt], cur[mt][0][s].z, cur[mt][1][s].z, cur[mt][0][s].w, cur[mt][1][s].w,
-                                 xq.z, xq.w);
-                    }
-                }
-            }
-            if (bn < nblk) {
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int hr = 0; hr < 2; ++hr)
-#pragma unroll
-                        for (int s = 0; s < 2; ++s) cur[mt][hr][s] = nxt[mt][hr][s];
-            }
-        }
-    }
-
-    // U^ h: one rank group (128 ranks) per warp iteration, group g -> warp g % HU_WARPS
-    {
-        const int ng = r >> 7;
-        const size_t rowb = static_cast<size_t>(r >> 1);
-        for (int g = warp; g < ng; g += HU_WARPS) {
-            uint32_t a[2][2][16];        // [m16 tile][row gid / gid+8][pair]: (code - zero) as bf16x2
-            float su[2][2];
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    const int m = m0 + mt * 16 + hr * 8 + gid;
-                    const uint4 q = ldg16_stream(uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
-                    const uint32_t z = uz[static_cast<size_t>(m) * ng + g];
-                    const uint32_t zz = kBf2_128 | z | (z << 16);
-                    su[mt][hr] = bf16_bits_to_f32(us[static_cast<size_t>(m) * ng + g]);
-                    const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int wi = 0; wi < 4; ++wi) {
-                        uint32_t e[4];
-                        unpack8_bf16(cw[wi], e);
-#pragma unroll
-                        for (int p = 0; p < 4; ++p) a[mt][hr][4 * wi + p] = bf2_sub(e[p], zz);
-                    }
-                }
-            const int kb = g * 128 + tig * 32;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int tok = nt * 8 + gid;
-                float pa[2][4];
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) pa[mt][i] = 0.f;
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    uint4 hq = make_uint4(0u, 0u, 0u, 0u);
-                    if (tok < T) hq = ldg16(h + static_cast<size_t>(tok) * r + kb + 8 * wi);
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        mma_bf16(pa[mt], a[mt][0][4 * wi], a[mt][1][4 * wi], a[mt][0][4 * wi + 1], a[mt][1][4 * wi + 1],
-                                 hq.x, hq.y);
-                        mma_bf16(pa[mt], a[mt][0][4 * wi + 2], a[mt][1][4 * wi + 2], a[mt][0][4 * wi + 3],
-                                 a[mt][1][4 * wi + 3], hq.z, hq.w);
-                    }
-                }
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {          // one rescale per group
-                    acc[mt][nt][0] += su[mt][0] * pa[mt][0];
-                    acc[mt][nt][1] += su[mt][0] * pa[mt][1];
-                    acc[mt][nt][2] += su[mt][1] * pa[mt][2];
-                    acc[mt][nt][3] += su[mt][1] * pa[mt][3];
-                }
-            }
-        }
-    }
-
-    // fixed-order reduction over the warps and store, 32 tokens at a time
+// Sum the 8 warps' partial tiles in a fixed order.  acc[mt][nt][4] covers 32 rows x 8*NT tokens;
+// sink(row, token, sum) is called once per element by exactly one thread.
+template <int NT, class Sink>
+__device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (&acc)[2][NT][4], int warp, int gid,
+                                             int tig, Sink sink) {
 #pragma unroll
     for (int b = 0; b < (NT + 3) / 4; ++b) {
 #pragma unroll
@@ -278,19 +87,301 @@ hu_kernel(const __nv_bfloat16* __restrict__ w_b, const __nv_bfloat16* __restrict
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int e = threadIdx.x + i * HU_THREADS;
+            const int e = threadIdx.x + i * FA_THREADS;
             const int row = e & 31, tok = e >> 5;
-            const int t = b * 32 + tok;
-            if (tok < 8 * (NT - 4 * b) && t < T) {
+            if (tok < 8 * (NT - 4 * b)) {
                 float s = 0.f;
 #pragma unroll
-                for (int w = 0; w < HU_WARPS; ++w) s += red[w][tok][row];
-                const size_t o = static_cast<size_t>(t) * M + m0 + row;
-                if (!FUSE_WB) s += __bfloat162float(y_dense[o]);
-                out[o] = __float2bfloat16_rn(s);
+                for (int w = 0; w < FA_WARPS; ++w) s += red[w][tok][row];
+                sink(row, b * 32 + tok, s);
             }
         }
         __syncthreads();
+    }
+}
+
+template <int NT>
+__device__ __forceinline__ void zero_acc(float (&acc)[2][NT][4]) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// phase A: h for the 16 ranks k0 .. k0+15; the d_i axis is split over the warps in chunks of 128.
+// ---------------------------------------------------------------------------------------------
+template <int NT>
+__device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32][33], int k0, int warp, int gid,
+                                        int tig) {
+    const int N = p.N, T = p.T;
+    const int g = k0 >> 7;
+    const size_t rowb = static_cast<size_t>(N >> 1);
+    const uint8_t* row0 = p.vt + static_cast<size_t>(k0 + gid) * rowb;
+    const uint8_t* row1 = row0 + 8 * rowb;
+    float acc[2][NT][4];             // only [0] is used; [1] stays zero so that the shared reducer applies
+    zero_acc<NT>(acc);
+    const int nchunks = N >> 7;
+    for (int c = warp; c < nchunks; c += FA_WARPS) {
+        const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
+        const uint4 q0 = ldg16_stream(row0 + (nb >> 1));
+        const uint4 q1 = ldg16_stream(row1 + (nb >> 1));
+        const uint16_t* sp = p.vs + static_cast<size_t>(g) * N + nb;
+        const uint8_t* zp = p.vz + static_cast<size_t>(g) * N + nb;
+        const uint4 s0 = ldg16(sp), s1 = ldg16(sp + 8), s2 = ldg16(sp + 16), s3 = ldg16(sp + 24);
+        const uint4 z0 = ldg16(zp), z1 = ldg16(zp + 16);
+        const uint32_t cw0[4] = {q0.x, q0.y, q0.z, q0.w};
+        const uint32_t cw1[4] = {q1.x, q1.y, q1.z, q1.w};
+        const uint32_t sw[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w,
+                                 s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
+        const uint32_t zw[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {                  // 8 columns per packed word
+            uint32_t e0[4], e1[4], a0[4], a1[4];
+            unpack8_bf16(cw0[wi], e0);
+            unpack8_bf16(cw1[wi], e1);
+            const uint32_t zz[4] = {__byte_perm(zw[2 * wi], 0x43434343u, 0x4140),
+                                    __byte_perm(zw[2 * wi], 0x43434343u, 0x4342),
+                                    __byte_perm(zw[2 * wi + 1], 0x43434343u, 0x4140),
+                                    __byte_perm(zw[2 * wi + 1], 0x43434343u, 0x4342)};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {                 // (code - zero) is exact; one rounding in the product
+                a0[q] = bf2_mul(bf2_sub(e0[q], zz[q]), sw[4 * wi + q]);
+                a1[q] = bf2_mul(bf2_sub(e1[q], zz[q]), sw[4 * wi + q]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int tok = nt * 8 + gid;
+                uint4 xq = make_uint4(0u, 0u, 0u, 0u);
+                if (tok < T) xq = ldg16(p.x + static_cast<size_t>(tok) * N + nb + 8 * wi);
+                mma_bf16(acc[0][nt], a0[0], a1[0], a0[1], a1[1], xq.x, xq.y);
+                mma_bf16(acc[0][nt], a0[2], a1[2], a0[3], a1[3], xq.z, xq.w);
+            }
+        }
+    }
+    __nv_bfloat16* h = p.h;
+    const int r = p.r;
+    reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) {
+        if (row < 16 && t < T) h[static_cast<size_t>(t) * r + k0 + row] = __float2bfloat16_rn(s);
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
+// phase W: acc += W_b[rows] x^T over this warp's share of the d_i axis (blocks of 64 columns,
+// block b -> warp b % 8), weights and activations loaded DEPTH-1 blocks ahead.
+// ---------------------------------------------------------------------------------------------
+template <int NT, int DEPTH, bool PREFETCH_X>
+__device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
+                                         int warp, int gid, int tig) {
+    const int N = p.N, T = p.T;
+    const int nblk = N >> 6;
+    const int cnt = (nblk - warp + FA_WARPS - 1) / FA_WARPS;        // blocks of this warp
+    const __nv_bfloat16* wrow[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);     // rows past the slice: re-read the last one
+            wrow[mt][hr] = p.w_b + static_cast<size_t>(m) * N + tig * 8;
+        }
+    const __nv_bfloat16* xrow[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xrow[nt] = p.x + static_cast<size_t>(min(nt * 8 + gid, T - 1)) * N + tig * 8;
+
+    uint4 A[DEPTH][2][2][2];
+    uint4 X[PREFETCH_X ? DEPTH : 1][NT][2];
+    auto load = [&](int d, int i) {
+        const int col = (warp + FA_WARPS * i) * 64;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr)
+#pragma unroll
+                for (int s = 0; s < 2; ++s) A[d][mt][hr][s] = ldg16_stream(wrow[mt][hr] + col + s * 32);
+        if (PREFETCH_X) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int s = 0; s < 2; ++s) X[d][nt][s] = ldg16(xrow[nt] + col + s * 32);
+        }
+    };
+    auto compute = [&](int d, int i) {
+        const int col = (warp + FA_WARPS * i) * 64;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const bool live = nt * 8 + gid < T;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                uint4 xq = PREFETCH_X ? X[d][nt][s] : ldg16(xrow[nt] + col + s * 32);
+                if (!live) xq = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma_bf16(acc[mt][nt], A[d][mt][0][s].x, A[d][mt][1][s].x, A[d][mt][0][s].y, A[d][mt][1][s].y,
+                             xq.x, xq.y);
+                    mma_bf16(acc[mt][nt], A[d][mt][0][s].z, A[d][mt][1][s].z, A[d][mt][0][s].w, A[d][mt][1][s].w,
+                             xq.z, xq.w);
+                }
+            }
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d)
+        if (d < cnt) load(d, d);
+    for (int i = 0; i < cnt; i += DEPTH) {
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) {
+            const int ii = i + d;
+            if (ii < cnt) {
+                if (ii + DEPTH - 1 < cnt) load((d + DEPTH - 1) % DEPTH, ii + DEPTH - 1);
+                compute(d, ii);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// phase U: acc += sum_g us * (Ucode - uz)[rows, group g] h^T, one rank group per warp iteration.
+// ---------------------------------------------------------------------------------------------
+template <int NT>
+__device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
+                                         int warp, int gid, int tig) {
+    const int T = p.T, r = p.r;
+    const int ng = r >> 7;
+    const size_t rowb = static_cast<size_t>(r >> 1);
+    for (int g = warp; g < ng; g += FA_WARPS) {
+        uint32_t a[2][2][16];        // [m16 tile][row gid / gid+8][pair]: (code - zero) as bf16x2
+        float su[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
+                const uint4 q = ldg16_stream(p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
+                const uint32_t z = p.uz[static_cast<size_t>(m) * ng + g];
+                const uint32_t zz = kBf2_128 | z | (z << 16);
+                su[mt][hr] = bf16_bits_to_f32(p.us[static_cast<size_t>(m) * ng + g]);
+                const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    uint32_t e[4];
+                    unpack8_bf16(cw[wi], e);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) a[mt][hr][4 * wi + q4] = bf2_sub(e[q4], zz);
+                }
+            }
+        const int kb = g * 128 + tig * 32;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int tok = nt * 8 + gid;
+            float pa[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pa[mt][i] = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                uint4 hq = make_uint4(0u, 0u, 0u, 0u);
+                if (tok < T) hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma_bf16(pa[mt], a[mt][0][4 * wi], a[mt][1][4 * wi], a[mt][0][4 * wi + 1], a[mt][1][4 * wi + 1],
+                             hq.x, hq.y);
+                    mma_bf16(pa[mt], a[mt][0][4 * wi + 2], a[mt][1][4 * wi + 2], a[mt][0][4 * wi + 3],
+                             a[mt][1][4 * wi + 3], hq.z, hq.w);
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {              // one rescale per group
+                acc[mt][nt][0] += su[mt][0] * pa[mt][0];
+                acc[mt][nt][1] += su[mt][0] * pa[mt][1];
+                acc[mt][nt][2] += su[mt][1] * pa[mt][2];
+                acc[mt][nt][3] += su[mt][1] * pa[mt][3];
+            }
+        }
+    }
+}
+
+template <int NT, bool FUSE_WB>
+__global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredParams p) {
+    extern __shared__ float fsmem[];
+    float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(fsmem);
+    constexpr int YS = 8 * NT + 1;                         // padded row stride of the y buffer
+    float* ybuf = fsmem + FA_WARPS * 32 * 33;              // [rows_cap][YS]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int G = gridDim.x, c = blockIdx.x;
+    const int row0 = static_cast<int>(static_cast<long long>(p.M) * c / G);
+    const int row1 = static_cast<int>(static_cast<long long>(p.M) * (c + 1) / G);
+    const int n_units = p.r >> 4;
+
+    // ---- phase A: units are dealt from the last CTA backwards (those CTAs own the fewest rows)
+    {
+        unsigned int done = 0;
+        for (int u = G - 1 - c; u < n_units; u += G) {
+            xv_unit<NT>(p, red, u * 16, warp, gid, tig);
+            ++done;
+        }
+        if (done) {                                        // uniform per CTA
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                __threadfence();
+                atomicAdd(p.sync, done);
+            }
+        }
+    }
+
+    // ---- phase W
+    if (FUSE_WB) {
+        for (int blk = row0; blk < row1; blk += FA_ROWS) {
+            float acc[2][NT][4];
+            zero_acc<NT>(acc);
+            constexpr int DEPTH = NT <= 2 ? 3 : 2;
+            wx_block<NT, DEPTH, (NT <= 4)>(p, acc, blk, row1, warp, gid, tig);
+            float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
+            reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) { yb[row * YS + t] = s; });
+        }
+    }
+
+    // ---- wait for every h unit (bounded; on expiry record a status and carry on)
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        while (ld_acquire_gpu(p.sync) < static_cast<unsigned int>(n_units)) {
+            if (clock64() - t0 > FA_SPIN_LIMIT) {
+                atomicExch(p.sync + 2, 1u);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- phase U and store
+    for (int blk = row0; blk < row1; blk += FA_ROWS) {
+        float acc[2][NT][4];
+        zero_acc<NT>(acc);
+        uh_block<NT>(p, acc, blk, row1, warp, gid, tig);
+        const float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
+        const int T = p.T, M = p.M;
+        const __nv_bfloat16* yd = p.y_dense;
+        __nv_bfloat16* out = p.out;
+        reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) {
+            const int m = blk + row;
+            if (m < row1 && t < T) {
+                const size_t o = static_cast<size_t>(t) * M + m;
+                s += FUSE_WB ? yb[row * YS + t] : __bfloat162float(yd[o]);
+                out[o] = __float2bfloat16_rn(s);
+            }
+        });
+    }
+
+    // ---- the last CTA to finish re-arms the counters for the next call on this scratch buffer
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {
+            atomicExch(p.sync, 0u);
+            atomicExch(p.sync + 1, 0u);
+        }
     }
 }
 

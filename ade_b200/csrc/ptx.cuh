@@ -131,6 +131,18 @@ __device__ __forceinline__ uint4 ldg16_stream(const void* p) {
     return v;
 }
 
+// 16-byte load served from L2 (never from this SM's L1): for data another CTA wrote during this kernel
+__device__ __forceinline__ uint4 ldcg16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // packed bf16x2 helpers on raw 32-bit registers
 __device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
     uint32_t d;

@@ -132,13 +132,28 @@ def _cdelta(p4: dict):
 _scratch: dict = {}
 
 
-def _scratch_for(dev: torch.device, stream_ptr: int, nbytes: int) -> torch.Tensor:
-    """Grow-only scratch per (device, stream): h = V^T x lives here between the two launches."""
-    key = (dev.index, stream_ptr)
+def _scratch_for(dev: torch.device, stream_ptr: int, T: int, r: int, nbytes: int) -> torch.Tensor:
+    """Scratch per (device, stream, T, r): h = V^T x and the kernel's three sync words, which must
+    start at zero and are left at zero by every completed call (so one zero-fill at allocation)."""
+    key = (dev.index, stream_ptr, T, r)
     buf = _scratch.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = _scratch[key] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+    if buf is None:
+        buf = _scratch[key] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
     return buf
+
+
+def factored_status(dev, T: int, r: int, stream_ptr: int | None = None) -> int:
+    """Status word of the scratch buffer used for (T, r) on `dev` (0 = every wait completed).
+    Synchronises the device."""
+    dev = torch.device(dev)
+    if stream_ptr is None:
+        with torch.cuda.device(dev):
+            stream_ptr = torch.cuda.current_stream().cuda_stream
+    buf = _scratch.get((dev.index if dev.index is not None else torch.cuda.current_device(), stream_ptr, T, r))
+    if buf is None:
+        return 0
+    off = _lib.load().ade_b200_factored_sync_offset(T, r)
+    return int(buf[off:off + 12].view(torch.int32)[2].item())
 
 
 def _check_x(x: torch.Tensor, N: int, what: str):
@@ -168,7 +183,7 @@ def factored_forward(x: torch.Tensor, p4: dict, weight: torch.Tensor | None = No
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
         nbytes = lib.ade_b200_factored_scratch_bytes(T, r)
-        scratch = _scratch_for(x.device, stream, nbytes)
+        scratch = _scratch_for(x.device, stream, T, r, nbytes)
         rc = lib.ade_b200_factored(
             ctypes.byref(_cdelta(p4)), x.data_ptr(),
             None if y_dense is None else y_dense.data_ptr(),

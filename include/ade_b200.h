@@ -103,12 +103,19 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
  * src/kernels.py:1182-1200), or sum_n w_b[m][n] x[t][n] computed inside the same kernel
  * when w_b != NULL (exactly one of the two must be given).
  *   x bf16 [T][N], y_dense bf16 [T][M], w_b bf16 [M][N], out bf16 [T][M].
- *   scratch: device buffer of at least ade_b200_factored_scratch_bytes(T, r) bytes, holds
- *   h = V^T x between the two launches; contents need no initialisation.
- * Requirements: 1 <= T <= 128, M % 32 == 0, N % 128 == 0, r % 128 == 0.
- * Two kernels are launched on `stream`; the call does not synchronise.
+ *   scratch: device buffer of at least ade_b200_factored_scratch_bytes(T, r) bytes.  It holds
+ *   h = V^T x (bf16 [T][r]) and, at byte offset ade_b200_factored_sync_offset(T, r), three
+ *   32-bit words used to order the phases of the kernel: they must be ZERO before the first
+ *   call that uses the buffer (one cudaMemset after allocation) and are left zero by every
+ *   call that completes normally, so the buffer can be reused call after call.  Word 2 is a
+ *   status word: it becomes 1 if the kernel's bounded wait for h expired (output undefined;
+ *   zero the three words before reusing the buffer).  Calls that share a scratch buffer must
+ *   not overlap on the GPU (use one buffer per stream).
+ * Requirements: 1 <= T <= 128, M >= 1 (at most 320 rows per SM), N % 128 == 0, r % 128 == 0.
+ * One kernel is launched on `stream` (one CTA per SM); the call does not synchronise.
  */
 size_t ade_b200_factored_scratch_bytes(int T, int r);
+size_t ade_b200_factored_sync_offset(int T, int r);
 int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b,
                       void* out, void* scratch, size_t scratch_bytes, int T, void* stream);
 

@@ -105,7 +105,8 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert lib.ade_b200_version() >= 1
-    assert lib.ade_b200_factored_scratch_bytes(16, 256) >= 16 * 256 * 2
+    assert lib.ade_b200_factored_scratch_bytes(16, 256) >= 16 * 256 * 2 + 12
+    assert lib.ade_b200_factored_sync_offset(16, 256) == lib.ade_b200_factored_scratch_bytes(16, 256) - 256
     assert lib.ade_b200_factored_scratch_bytes(0, 256) == 0
 
 
