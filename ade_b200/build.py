@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libade_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false",
+    "-shared", "-Xcompiler", "-fPIC",
 ]
 
 
@@ -30,8 +30,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and all(os.path.getmtime(LIB) >= os.path.getmtime(s) for s in sources()):
         return LIB
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
-    cmd = [nvcc, *flags, *(["-Xptxas", "-v"] if verbose else []), os.path.join(CSRC, "ade_b200.cu"), "-o", LIB + ".tmp"]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), os.path.join(CSRC, "ade_b200.cu"), "-o", LIB + ".tmp"]
     subprocess.run(cmd, check=True)
     os.replace(LIB + ".tmp", LIB)
     return LIB

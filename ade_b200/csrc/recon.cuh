@@ -7,28 +7,35 @@
 //
 // One persistent CTA per SM walks 128 x 128 output tiles.  Warp roles:
 //   warps 0-7   epilogue: tcgen05.ld of P_g, float conversion, per-group rescale in FP32
-//               registers (64 accumulators per thread), base add, bf16 store.  Warp w owns
-//               tensor-memory lanes 32*(w%4).. and columns 64*(w/4)..
-//   warps 8-11  unpack: 128-bit loads of the nibble-packed codes, expand to signed int8 with
-//               the zero-point subtracted, write K-major 128-byte-swizzled operand tiles.
+//               registers (64 accumulators per thread, packed two per 64-bit register), base
+//               add, bf16 store.  Warp w owns tensor-memory lanes 32*(w%4).. and columns 64*(w/4)..
+//               The base tile comes in and the merged tile goes out through a shared-memory
+//               tile buffer so that every global access is a full 128-byte line (a thread owns a
+//               row of the accumulator, but a warp moves two whole rows per instruction).
+//   warps 8-11  unpack: the nibble-packed codes arrive through a per-thread cp.async ring four
+//               work items deep (global latency never stalls the ring), are expanded to signed
+//               int8 with the zero-point subtracted and written as K-major 128-byte-swizzled
+//               operand tiles.
 //   warp  12    one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group and
 //               commits to mbarriers; it also owns the tensor-memory allocation.
-// Rings: 3 operand stages in shared memory (32 KB each), 2 accumulator stages in tensor
-// memory (128 columns each).  Every mbarrier wait is bounded: when it expires the kernel
-// raises a shared abort flag, records a code in *status, lets every later wait fall through
-// and still runs to its normal end (tensor memory is released, no trap).
+// Rings: 4 raw code items and 2 operand stages (32 KB each) in shared memory, 2 accumulator
+// stages in tensor memory (128 columns each).  Every mbarrier wait is bounded: when it expires the
+// kernel raises a shared abort flag, records a code in *status, lets every later wait fall
+// through and still runs to its normal end (tensor memory is released, no trap).
 #pragma once
 #include "ptx.cuh"
 
 namespace ade {
 
 constexpr int RC_TILE = 128;
-constexpr int RC_STAGES = 3;
-constexpr int RC_STAGE_BYTES = 2 * RC_TILE * 128;      // A tile + B tile, 128 int8 per row
+constexpr int RC_STAGES = 2;                            // int8 operand stages
+constexpr int RC_STAGE_BYTES = 2 * RC_TILE * 128;       // A tile + B tile, 128 int8 per row
 constexpr int RC_EPI_THREADS = 256;
 constexpr int RC_PROD_THREADS = 128;
 constexpr int RC_THREADS = RC_EPI_THREADS + RC_PROD_THREADS + 32;
 constexpr int RC_TMEM_COLS = 256;
+constexpr int RC_RAW_DEPTH = 3;                         // raw code items in flight per unpack thread
+constexpr int RC_RAW_ITEM = RC_PROD_THREADS * (8 * 16 + 8 * 4);   // per item: 8 x 16 B codes + 8 x 4 B zero words
 constexpr long long RC_SPIN_LIMIT = 2000000000LL;       // clock cycles (about one second)
 // instruction descriptor: D = S32 (bits 4-5 = 2), A = B = signed 8-bit (bits 7-9, 10-12 = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 = 16 (bits 17-22), M >> 4 = 8 (bits 24-28)
@@ -48,12 +55,13 @@ struct ReconParams {
     int M, N, r;
 };
 
-constexpr int RC_WB_SLOT = 144;                         // 128 bytes of W_b per epilogue thread, padded (bank spread)
-constexpr int RC_WB_BYTES = RC_EPI_THREADS * RC_WB_SLOT;
+constexpr int RC_WB_ROW = 272;                          // one tile row: 256 bytes of bf16, padded (bank spread)
+constexpr int RC_WB_BYTES = 2 * RC_TILE * RC_WB_ROW;    // two tile buffers (base in, merged out)
 
 __host__ __device__ inline size_t recon_smem_bytes(int ng) {
-    return 1024 /* alignment slack */ + static_cast<size_t>(RC_STAGES) * RC_STAGE_BYTES + RC_WB_BYTES +
-           static_cast<size_t>(4) * ng * RC_TILE * sizeof(float) + 256;
+    return 1024 /* alignment slack */ + static_cast<size_t>(RC_STAGES) * RC_STAGE_BYTES +
+           static_cast<size_t>(RC_RAW_DEPTH) * RC_RAW_ITEM + RC_WB_BYTES +
+           static_cast<size_t>(2) * ng * RC_TILE * (sizeof(float) + sizeof(uint16_t)) + 256;
 }
 
 __device__ __forceinline__ void wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
@@ -70,9 +78,22 @@ __device__ __forceinline__ void wait_bounded(uint32_t bar, uint32_t parity, vola
     }
 }
 
-// 32 packed codes (one 16-byte load) of operand row `row`, 16-byte column c of the packed row:
-// expand to 32 signed bytes (code - zero) and store them as logical 16-byte chunks 2c, 2c+1 of
-// the 128-byte row, XOR-swizzled with the row index as the 128-byte swizzle mode expects.
+// cp.async with zero fill: copies 16 (or 4) bytes when live, writes zeros otherwise
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4_zfill(uint32_t dst, const void* src, bool live) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(live ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// 32 packed codes (16 bytes) of operand row `row`, 16-byte column c of the packed row: expand to
+// 32 signed bytes (code - zero) and store them as logical 16-byte chunks 2c, 2c+1 of the
+// 128-byte row, XOR-swizzled with the row index as the 128-byte swizzle mode expects.
 __device__ __forceinline__ void unpack_store(uint8_t* tile, int row, int c, uint4 q, uint32_t z) {
     const uint32_t zk = 0x80808080u - z * 0x01010101u;   // per byte 0x80 - zero, no borrow (zero <= 15)
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -90,29 +111,42 @@ __device__ __forceinline__ void unpack_store(uint8_t* tile, int row, int c, uint
     *reinterpret_cast<uint4*>(rp + (((2 * c + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-struct ProdRegs {
-    uint4 qa[4], qb[4];
-    uint32_t za[4], zb[4];
+// Position of one unpack thread in the (tile, group) sequence of its CTA, with the addresses of
+// the first of its four rows per operand (the other three are 32 rows further each).
+struct ProdCursor {
+    const uint8_t* ua;      // codes of U
+    const uint8_t* vb;      // codes of V
+    const uint8_t* uzp;     // zero-points of the U row
+    const uint8_t* vzp;     // zero-points of the V column, group 0
+    int tile, g, m_first;
 };
 
-__device__ __forceinline__ void prod_load(ProdRegs& R, const ReconParams& p, int ng, int m0, int n0, int g, int rbase,
-                                          int c) {
+__device__ __forceinline__ void cursor_set_tile(ProdCursor& c, const ReconParams& p, int ng, int tiles_n, int rbase,
+                                                int cc) {
     const size_t rowb = static_cast<size_t>(p.r >> 1);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int row = rbase + 32 * i;
-        const int m = m0 + row, n = n0 + row;
-        if (m < p.M) {
-            R.qa[i] = ldg16(p.uq + static_cast<size_t>(m) * rowb + g * 64 + c * 16);
-            R.za[i] = p.uz[static_cast<size_t>(m) * ng + g];
-        } else {
-            R.qa[i] = make_uint4(0u, 0u, 0u, 0u);
-            R.za[i] = 0u;
-        }
-        R.qb[i] = ldg16(p.vq + static_cast<size_t>(n) * rowb + g * 64 + c * 16);
-        R.zb[i] = p.vz[static_cast<size_t>(g) * p.N + n];
-    }
+    const int m0 = (c.tile / tiles_n) << 7, n0 = (c.tile % tiles_n) << 7;
+    c.m_first = m0 + rbase;
+    c.ua = p.uq + static_cast<size_t>(c.m_first) * rowb + cc * 16;
+    c.uzp = p.uz + static_cast<size_t>(c.m_first) * ng;
+    c.vb = p.vq + static_cast<size_t>(n0 + rbase) * rowb + cc * 16;
+    c.vzp = p.vz + n0 + rbase;
+    c.g = 0;
 }
+
+#ifdef ADE_PHASE_PROF
+__device__ long long g_recon_prof[256 * 16];
+#define RC_T0() const long long t0_ = clock64()
+#define RC_ACC(var) var += clock64() - t0_
+#define RC_DECL(var) long long var = 0
+#define RC_PUT(i, var) g_recon_prof[blockIdx.x * 16 + (i)] = (var)
+#define RC_LAP(k) do { const long long n_ = clock64(); seg_[k] += n_ - lap_; lap_ = n_; } while (0)
+#else
+#define RC_T0()
+#define RC_ACC(var)
+#define RC_DECL(var)
+#define RC_PUT(i, var)
+#define RC_LAP(k)
+#endif
 
 // DBG = true additionally dumps every P_g to p.dbg (test builds of the launch only).
 template <bool DBG>
@@ -121,15 +155,15 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int ng = p.r >> 7;
     uint8_t* stage_base = smem;
-    uint8_t* wb_stage = smem + RC_STAGES * RC_STAGE_BYTES;                            // [256][144]
-    float* sc = reinterpret_cast<float*>(wb_stage + RC_WB_BYTES);                     // [2][u|v][ng][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 4 * ng * RC_TILE);
+    uint8_t* raw_ring = smem + RC_STAGES * RC_STAGE_BYTES;                            // [RC_RAW_DEPTH][RC_RAW_ITEM]
+    uint8_t* wb_stage = raw_ring + RC_RAW_DEPTH * RC_RAW_ITEM;                        // [2][128][272]
+    float* sc = reinterpret_cast<float*>(wb_stage + RC_WB_BYTES);     // float32 [u|v][ng][128], then bf16 raw copy
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 3 * ng * RC_TILE);
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8 * RC_STAGES;
     const uint32_t tfull0 = empty0 + 8 * RC_STAGES;
     const uint32_t tempty0 = tfull0 + 16;
-    const uint32_t wbfull = tempty0 + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * RC_STAGES + 5);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * RC_STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,7 +176,6 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
             mbar_init(tfull0 + 8 * a, 1);
             mbar_init(tempty0 + 8 * a, RC_EPI_THREADS);
         }
-        mbar_init(wbfull, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -164,128 +197,274 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
         const int row = q * 32 + lane;
         const int et = threadIdx.x;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * 64;
+        const int crow = et >> 4, cck = et & 15;         // coalesced tile access: 16 threads per 256-byte row
+        const int nsc = 2 * ng * RC_TILE;                // scale values per tile: [u | v][ng][128]
+        float* su = sc;                                  // float32 scales of the current tile
+        float* sv = sc + ng * RC_TILE;
+        const uint16_t* raw_u = reinterpret_cast<const uint16_t*>(sc + nsc);          // bf16 [128 rows][ng], next tile
+        const uint16_t* raw_v = raw_u + ng * RC_TILE;                                 // bf16 [ng][128]
+        const uint32_t raw_s = smem_u32(raw_u);
+        // Scales of a tile are two contiguous pieces of global memory per group at most: rows m0.. of us
+        // (128 * ng values in one run) and 128 values of vs per group.  They are copied with cp.async
+        // one tile ahead and converted to float32 at the start of their tile.
+        auto issue_scales = [&](int tile) {
+            if (tile < ntiles) {
+                const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
+                const int npieces = 32 * ng;             // 16-byte pieces: 16 * ng of us, then 16 per group of vs
+                for (int j = et; j < npieces; j += RC_EPI_THREADS) {
+                    if (j < 16 * ng) {
+                        const long long off = (static_cast<long long>(m0) * ng) * 2 + j * 16;
+                        const long long left = static_cast<long long>(p.M) * ng * 2 - off;
+                        const int nbytes = left >= 16 ? 16 : (left > 0 ? static_cast<int>(left) : 0);
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.us) + (nbytes ? off : 0);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(raw_s + j * 16), "l"(src), "r"(nbytes)
+                                     : "memory");
+                    } else {
+                        const int jj = j - 16 * ng, g = jj >> 4, piece = jj & 15;
+                        cp_async16_zfill(raw_s + j * 16, p.vs + static_cast<size_t>(g) * p.N + n0 + piece * 8, true);
+                    }
+                }
+            }
+            cp_async_commit_group();
+        };
+        issue_scales(blockIdx.x);
+
         uint32_t it = 0, tcount = 0;
+        RC_DECL(w_tfull); RC_DECL(w_bar); RC_DECL(w_wb);
+#ifdef ADE_PHASE_PROF
+        long long seg_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+#ifdef ADE_PHASE_PROF
+        const long long tstart_ = clock64();
+#endif
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
             const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
             const int m = m0 + row;
             const bool live = m < p.M;
-            float* su = sc + (tcount & 1) * (2 * ng * RC_TILE);
-            float* sv = su + ng * RC_TILE;
-            for (int e = et; e < ng * RC_TILE; e += RC_EPI_THREADS) {
-                const int g = e >> 7, i = e & 127;
-                const int mm = m0 + i;
-                su[e] = mm < p.M ? bf16_bits_to_f32(p.us[static_cast<size_t>(mm) * ng + g]) : 0.f;
-                sv[e] = bf16_bits_to_f32(p.vs[static_cast<size_t>(g) * p.N + n0 + i]);
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");
-
-            // this thread's 128 bytes of the base row, copied asynchronously into its own slot
-            const size_t obase = static_cast<size_t>(m) * p.N + n0 + hh * 64;
-            uint8_t* slot = wb_stage + et * RC_WB_SLOT;
-            if (et == 0) {
-                const int live_rows = min(RC_TILE, p.M - m0);
-                mbar_arrive_expect_tx(wbfull, static_cast<uint32_t>(live_rows) * 256u);
-            }
-            if (live) {
-                fence_proxy_async_smem();                // last tile's reads of the slot precede the new copy
-                bulk_g2s(smem_u32(slot), p.wb + obase, 128u, wbfull);
-            }
-
-            float acc[64];
+#ifdef ADE_PHASE_PROF
+            const long long tp0_ = clock64();
+            long long lap_ = tp0_;
+#endif
+            // base tile -> shared memory, two whole rows per warp instruction
+            uint8_t* wbuf = wb_stage + (tcount & 1) * (RC_TILE * RC_WB_ROW);
+            const uint32_t wbuf_s = smem_u32(wbuf);
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+            for (int j = 0; j < 8; ++j) {
+                const int r_ = j * 16 + crow;
+                const bool lv = m0 + r_ < p.M;
+                cp_async16_zfill(wbuf_s + r_ * RC_WB_ROW + cck * 16,
+                                 p.wb + static_cast<size_t>(lv ? m0 + r_ : 0) * p.N + n0 + cck * 8, lv);
+            }
+            cp_async_commit_group();
+            RC_LAP(0);
+            // scales of this tile were copied during the previous one: convert them to float32
+            cp_async_wait_group<1>();                    // all but the base tile just issued
+            RC_LAP(1);
+            asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // copies visible, old scales unused
+            for (int e = et; e < nsc; e += RC_EPI_THREADS) {
+                const int ee = e < ng * RC_TILE ? e : e - ng * RC_TILE;
+                const int g = ee >> 7, i = ee & 127;
+                su[e] = bf16_bits_to_f32(e < ng * RC_TILE ? raw_u[i * ng + g] : raw_v[g * RC_TILE + i]);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // float32 scales complete
+            RC_LAP(2);
+            issue_scales(tile + gridDim.x);              // next tile's scales, consumed one tile later
+
+            RC_LAP(3);
+#ifdef ADE_PHASE_PROF
+            w_bar += clock64() - tp0_;
+#endif
+            uint64_t acc[32];                            // 64 float32 accumulators as packed pairs
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                wait_bounded(tfull0 + 8 * a, aph, abort_flag, p.status, 3);
+                { RC_T0(); wait_bounded(tfull0 + 8 * a, aph, abort_flag, p.status, 3); RC_ACC(w_tfull); }
                 tc_fence_after();
                 const float u = su[g * RC_TILE + row];
+                const uint64_t uu = f2_pack(u, u);
+                const uint32_t tbase = lane_addr + a * RC_TILE;
+                const ulonglong2* svp = reinterpret_cast<const ulonglong2*>(sv + g * RC_TILE + hh * 64);
+                uint32_t v[2][16];                       // two 16-column chunks in flight
+                tmem_ld16(tbase, v[0]);
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + a * RC_TILE + ch * 32, v);
+                for (int ch = 0; ch < 4; ++ch) {
                     tmem_ld_wait();
-                    if (ch == 1) {                       // accumulator stage is in registers: hand it back
+                    if (ch < 3) tmem_ld16(tbase + (ch + 1) * 16, v[(ch + 1) & 1]);
+                    if (ch == 3) {                       // accumulator stage is in registers: hand it back
                         tc_fence_before();
                         mbar_arrive(tempty0 + 8 * a);
                     }
-                    const float4* svp = reinterpret_cast<const float4*>(sv + g * RC_TILE + hh * 64 + ch * 32);
+                    const uint32_t (&vc)[16] = v[ch & 1];
 #pragma unroll
-                    for (int i4 = 0; i4 < 8; ++i4) {
-                        const float4 f = svp[i4];
-                        const float vv[4] = {f.x, f.y, f.z, f.w};
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        const ulonglong2 f = svp[ch * 4 + i4];            // column scales of 4 columns
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int i = i4 * 4 + j;
+                        for (int j = 0; j < 2; ++j) {
+                            const int i = i4 * 4 + j * 2;
                             // exact int -> float for |P| < 2^22: 1.5 * 2^23 + P has P in its mantissa
-                            const float pf = __fsub_rn(__int_as_float(static_cast<int>(v[i]) + 0x4B400000), 12582912.0f);
-                            const float s = __fmul_rn(u, vv[j]);
-                            acc[ch * 32 + i] = __fadd_rn(acc[ch * 32 + i], __fmul_rn(pf, s));
+                            const uint64_t pf = f2_add(f2_pack(__int_as_float(static_cast<int>(vc[i]) + 0x4B400000),
+                                                               __int_as_float(static_cast<int>(vc[i + 1]) + 0x4B400000)),
+                                                       neg_magic);
+#if defined(ADE_EXP) && ADE_EXP == 1
+                            acc[ch * 8 + i4 * 2 + j] ^= (static_cast<uint64_t>(vc[i]) << 32) | vc[i + 1];
+#elif defined(ADE_EXP) && ADE_EXP == 2
+                            acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], pf);
+#elif defined(ADE_EXP) && ADE_EXP == 3
+                            const uint64_t s2 = f2_mul(uu, j == 0 ? f.x : f.y);
+                            acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], f2_mul(pf, s2));
+#else
+                            const uint64_t s2 = f2_mul(uu, j == 0 ? f.x : f.y);      // us * vs, exact
+                            acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], f2_mul_rounded(pf, s2));
+#endif
                         }
                     }
                     if (DBG && live) {
-                        int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * 64 + ch * 32;
+                        int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * 64 + ch * 16;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<int4*>(d + i) = make_int4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        for (int i = 0; i < 16; i += 4)
+                            *reinterpret_cast<int4*>(d + i) = make_int4(vc[i], vc[i + 1], vc[i + 2], vc[i + 3]);
                     }
                 }
             }
-            wait_bounded(wbfull, tcount & 1, abort_flag, p.status, 5);
-            if (live) {
+#ifdef ADE_PHASE_PROF
+            const long long tf0_ = clock64();
+            lap_ = tf0_;
+#endif
+            cp_async_wait_group<1>();                    // this thread's pieces of the base tile have landed
+            RC_LAP(4);
+            asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // ... and everyone else's
+            RC_LAP(5);
+            {
+                uint8_t* own = wbuf + row * RC_WB_ROW + hh * 128;          // this thread's row segment
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(slot + j * 16);
+                    const uint4 wv = *reinterpret_cast<const uint4*>(own + j * 16);
                     const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
                     uint32_t oq[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float b0 = __uint_as_float(wq[e] << 16);
-                        const float b1 = __uint_as_float(wq[e] & 0xFFFF0000u);
-                        const __nv_bfloat162 o = __floats2bfloat162_rn(__fadd_rn(b0, acc[j * 8 + 2 * e]),
-                                                                       __fadd_rn(b1, acc[j * 8 + 2 * e + 1]));
+                        const uint64_t b2 = f2_pack(__uint_as_float(wq[e] << 16), __uint_as_float(wq[e] & 0xFFFF0000u));
+                        float o0, o1;
+                        f2_unpack(f2_add(b2, acc[j * 4 + e]), o0, o1);
+                        const __nv_bfloat162 o = __floats2bfloat162_rn(o0, o1);
                         oq[e] = *reinterpret_cast<const uint32_t*>(&o);
                     }
-                    *reinterpret_cast<uint4*>(p.out + obase + j * 8) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+                    *reinterpret_cast<uint4*>(own + j * 16) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
                 }
             }
+            RC_LAP(6);
+            asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // merged tile complete
+            RC_LAP(7);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r_ = j * 16 + crow;
+                if (m0 + r_ < p.M)
+                    *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(m0 + r_) * p.N + n0 + cck * 8) =
+                        *reinterpret_cast<const uint4*>(wbuf + r_ * RC_WB_ROW + cck * 16);
+            }
+#ifdef ADE_PHASE_PROF
+            w_wb += clock64() - tf0_;
+#endif
         }
+#ifdef ADE_PHASE_PROF
+        if (et == 0) { RC_PUT(0, w_tfull); RC_PUT(1, w_bar); RC_PUT(2, w_wb); RC_PUT(3, clock64() - tstart_);
+            for (int k = 0; k < 8; ++k) RC_PUT(8 + k, seg_[k]); }
+#endif
     } else if (warp < 12) {
         // ------------------------------------------------------------------ unpack producers
         const int pt = threadIdx.x - RC_EPI_THREADS;
         const int c = pt & 3, rbase = pt >> 2;
-        const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int my_tiles = static_cast<int>(blockIdx.x) < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int total = my_tiles * ng;
-        ProdRegs cur, nxt;
-        if (total > 0) prod_load(cur, p, ng, (blockIdx.x / tiles_n) << 7, (blockIdx.x % tiles_n) << 7, 0, rbase, c);
-        for (int idx = 0; idx < total; ++idx) {
-            if (idx + 1 < total) {
-                const int tile = blockIdx.x + ((idx + 1) / ng) * gridDim.x;
-                prod_load(nxt, p, ng, (tile / tiles_n) << 7, (tile % tiles_n) << 7, (idx + 1) % ng, rbase, c);
+        const size_t step = static_cast<size_t>(32) * (p.r >> 1);          // 32 rows further down a code array
+        const uint32_t raw_s = smem_u32(raw_ring);
+        ProdCursor ld, use;                               // issue position and consume position
+        ld.tile = use.tile = blockIdx.x;
+        if (total > 0) {
+            cursor_set_tile(ld, p, ng, tiles_n, rbase, c);
+            cursor_set_tile(use, p, ng, tiles_n, rbase, c);
+        }
+        auto advance = [&](ProdCursor& cur) {
+            if (++cur.g == ng) {
+                cur.tile += gridDim.x;
+                if (cur.tile < ntiles) cursor_set_tile(cur, p, ng, tiles_n, rbase, c);
             }
+        };
+        // one work item (tile, group) = 8 x 16 bytes of codes and 8 aligned words holding the zero-points
+        auto issue = [&](int idx) {
+            if (idx < total) {
+                const uint32_t base = raw_s + (idx % RC_RAW_DEPTH) * RC_RAW_ITEM;
+                const uint32_t cs = base + pt * 16, zs = base + RC_PROD_THREADS * 128 + pt * 4;
+                const int go = ld.g * 64;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const bool live = ld.m_first + 32 * i < p.M;           // rows past the matrix become zeros
+                    const size_t off = live ? i * step : 0;
+                    cp_async16_zfill(cs + i * (RC_PROD_THREADS * 16), ld.ua + off + go, live);
+                    cp_async16_zfill(cs + (4 + i) * (RC_PROD_THREADS * 16), ld.vb + i * step + go, true);
+                    const uint8_t* za = ld.uzp + (live ? static_cast<size_t>(32 * i) * ng : 0) + ld.g;
+                    cp_async4_zfill(zs + i * (RC_PROD_THREADS * 4),
+                                    reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(za) & ~uintptr_t(3)), live);
+                    const uint8_t* zb = ld.vzp + static_cast<size_t>(ld.g) * p.N + 32 * i;
+                    cp_async4_zfill(zs + (4 + i) * (RC_PROD_THREADS * 4),
+                                    reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(zb) & ~uintptr_t(3)), true);
+                }
+                advance(ld);
+            }
+            cp_async_commit_group();                     // one group per item slot, empty past the end
+        };
+        for (int i = 0; i < RC_RAW_DEPTH - 1; ++i) issue(i);
+        RC_DECL(w_cp); RC_DECL(w_empty);
+        for (int idx = 0; idx < total; ++idx) {
+            { RC_T0(); cp_async_wait_group<RC_RAW_DEPTH - 2>(); RC_ACC(w_cp); }     // item idx has landed
+            const uint8_t* base = raw_ring + (idx % RC_RAW_DEPTH) * RC_RAW_ITEM;
+            uint4 qa[4], qb[4];
+            uint32_t za[4], zb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                qa[i] = *reinterpret_cast<const uint4*>(base + (i * RC_PROD_THREADS + pt) * 16);
+                qb[i] = *reinterpret_cast<const uint4*>(base + ((4 + i) * RC_PROD_THREADS + pt) * 16);
+                const uint32_t wa =
+                    *reinterpret_cast<const uint32_t*>(base + RC_PROD_THREADS * 128 + (i * RC_PROD_THREADS + pt) * 4);
+                const uint32_t wz =
+                    *reinterpret_cast<const uint32_t*>(base + RC_PROD_THREADS * 128 + ((4 + i) * RC_PROD_THREADS + pt) * 4);
+                const uint32_t sa = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(use.uzp)) + 32u * i * ng + use.g) & 3u;
+                const uint32_t sb = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(use.vzp)) + 32u * i) & 3u;
+                za[i] = (wa >> (8 * sa)) & 0xFFu;         // zero-filled words of dead rows give 0
+                zb[i] = (wz >> (8 * sb)) & 0xFFu;
+            }
+            advance(use);
+            issue(idx + RC_RAW_DEPTH - 1);               // refill the slot consumed one iteration ago
             const uint32_t s = idx % RC_STAGES, ph = (idx / RC_STAGES) & 1;
-            wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 2);
+            { RC_T0(); wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 2); RC_ACC(w_empty); }
             uint8_t* A = stage_base + s * RC_STAGE_BYTES;
             uint8_t* B = A + RC_TILE * 128;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                unpack_store(A, rbase + 32 * i, c, cur.qa[i], cur.za[i]);
-                unpack_store(B, rbase + 32 * i, c, cur.qb[i], cur.zb[i]);
+                unpack_store(A, rbase + 32 * i, c, qa[i], za[i]);
+                unpack_store(B, rbase + 32 * i, c, qb[i], zb[i]);
             }
             fence_proxy_async_smem();
             mbar_arrive(full0 + 8 * s);
-            cur = nxt;
         }
+        cp_async_wait_group<0>();
+#ifdef ADE_PHASE_PROF
+        if (pt == 0) { RC_PUT(4, w_cp); RC_PUT(5, w_empty); }
+#endif
     } else {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t it = 0;
+            RC_DECL(w_full); RC_DECL(w_tempty);
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
                 for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t s = it % RC_STAGES, ph = (it / RC_STAGES) & 1;
                     const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                    wait_bounded(tempty0 + 8 * a, aph ^ 1, abort_flag, p.status, 4);
-                    wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1);
+                    { RC_T0(); wait_bounded(tempty0 + 8 * a, aph ^ 1, abort_flag, p.status, 4); RC_ACC(w_tempty); }
+                    { RC_T0(); wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1); RC_ACC(w_full); }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + s * RC_STAGE_BYTES);
                     const uint64_t ad = smem_desc_k_sw128(sa);
@@ -297,6 +476,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                     tc_commit(tfull0 + 8 * a);           // accumulator stage ready
                 }
             }
+            RC_PUT(6, w_full); RC_PUT(7, w_tempty);
         }
         __syncwarp();
     }

@@ -24,7 +24,7 @@ extern "C" {
 #endif
 
 #define ADE_B200_GROUP 128          /* ranks per quantization group (G); the only supported value */
-#define ADE_B200_MAX_RANK 4096
+#define ADE_B200_MAX_RANK 2048
 #define ADE_B200_MAX_TOKENS 128     /* largest T of the factored path (src/serving.py:105) */
 
 /* return codes */
