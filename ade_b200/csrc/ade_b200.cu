@@ -118,12 +118,6 @@ bool optin_factored() {
 
 }  // namespace
 
-#ifdef ADE_PHASE_PROF
-extern "C" int ade_b200_debug_recon_prof(long long* host_out, int count) {
-    return cudaMemcpyFromSymbol(host_out, ade::g_recon_prof, sizeof(long long) * count) == cudaSuccess ? 0 : -5;
-}
-#endif
-
 extern "C" {
 
 int ade_b200_version(void) { return 1; }

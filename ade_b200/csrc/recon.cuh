@@ -6,19 +6,21 @@
 // by the base add of src/serving.py:92.
 //
 // One persistent CTA per SM walks 128 x 128 output tiles.  Warp roles:
-//   warps 0-7   epilogue: tcgen05.ld of P_g, float conversion, per-group rescale in FP32
-//               registers (64 accumulators per thread, packed two per 64-bit register), base
-//               add, bf16 store.  Warp w owns tensor-memory lanes 32*(w%4).. and columns 64*(w/4)..
+//   warps 0-15  epilogue: tcgen05.ld of P_g, float conversion, per-group rescale in FP32
+//               registers (32 accumulators per thread, packed two per 64-bit register), base
+//               add, bf16 store.  Warp w owns tensor-memory lanes 32*(w%4).. and columns 32*(w/4)..
+//               Sixteen warps rather than eight with twice the registers: this stage is bound
+//               by issue latency, and four warps per scheduler hide it where two do not.
 //               The base tile comes in and the merged tile goes out through a shared-memory
 //               tile buffer so that every global access is a full 128-byte line (a thread owns a
 //               row of the accumulator, but a warp moves two whole rows per instruction).
-//   warps 8-11  unpack: the nibble-packed codes arrive through a per-thread cp.async ring four
+//   warps 16-19 unpack: the nibble-packed codes arrive through a per-thread cp.async ring three
 //               work items deep (global latency never stalls the ring), are expanded to signed
 //               int8 with the zero-point subtracted and written as K-major 128-byte-swizzled
 //               operand tiles.
-//   warp  12    one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group and
+//   warp  20    one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=128, K=32) per group and
 //               commits to mbarriers; it also owns the tensor-memory allocation.
-// Rings: 4 raw code items and 2 operand stages (32 KB each) in shared memory, 2 accumulator
+// Rings: 3 raw code items and 2 operand stages (32 KB each) in shared memory, 2 accumulator
 // stages in tensor memory (128 columns each).  Every mbarrier wait is bounded: when it expires the
 // kernel raises a shared abort flag, records a code in *status, lets every later wait fall
 // through and still runs to its normal end (tensor memory is released, no trap).
@@ -30,7 +32,10 @@ namespace ade {
 constexpr int RC_TILE = 128;
 constexpr int RC_STAGES = 2;                            // int8 operand stages
 constexpr int RC_STAGE_BYTES = 2 * RC_TILE * 128;       // A tile + B tile, 128 int8 per row
-constexpr int RC_EPI_THREADS = 256;
+constexpr int RC_EPI_WARPS = 16;                        // 4 lane quadrants x 4 column slices
+constexpr int RC_EPI_THREADS = RC_EPI_WARPS * 32;
+constexpr int RC_CW = RC_TILE / (RC_EPI_WARPS / 4);     // accumulator columns per epilogue thread
+constexpr int RC_MMA_WARP = RC_EPI_WARPS + 4;
 constexpr int RC_PROD_THREADS = 128;
 constexpr int RC_THREADS = RC_EPI_THREADS + RC_PROD_THREADS + 32;
 constexpr int RC_TMEM_COLS = 256;
@@ -133,21 +138,6 @@ __device__ __forceinline__ void cursor_set_tile(ProdCursor& c, const ReconParams
     c.g = 0;
 }
 
-#ifdef ADE_PHASE_PROF
-__device__ long long g_recon_prof[256 * 16];
-#define RC_T0() const long long t0_ = clock64()
-#define RC_ACC(var) var += clock64() - t0_
-#define RC_DECL(var) long long var = 0
-#define RC_PUT(i, var) g_recon_prof[blockIdx.x * 16 + (i)] = (var)
-#define RC_LAP(k) do { const long long n_ = clock64(); seg_[k] += n_ - lap_; lap_ = n_; } while (0)
-#else
-#define RC_T0()
-#define RC_ACC(var)
-#define RC_DECL(var)
-#define RC_PUT(i, var)
-#define RC_LAP(k)
-#endif
-
 // DBG = true additionally dumps every P_g to p.dbg (test builds of the launch only).
 template <bool DBG>
 __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams p) {
@@ -169,17 +159,17 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < RC_STAGES; ++s) {
-            mbar_init(full0 + 8 * s, RC_PROD_THREADS);
+            mbar_init(full0 + 8 * s, RC_PROD_THREADS / 32);
             mbar_init(empty0 + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, RC_EPI_THREADS);
+            mbar_init(tempty0 + 8 * a, RC_EPI_WARPS);
         }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 12) {
+    if (warp == RC_MMA_WARP) {
         tmem_alloc(smem_u32(tmem_slot), RC_TMEM_COLS);
         tmem_relinquish();
     }
@@ -191,12 +181,12 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
     const int tiles_n = p.N >> 7;
     const int ntiles = ((p.M + RC_TILE - 1) >> 7) * tiles_n;
 
-    if (warp < 8) {
+    if (warp < RC_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
         const int q = warp & 3, hh = warp >> 2;
         const int row = q * 32 + lane;
         const int et = threadIdx.x;
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * 64;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * RC_CW;
         const int crow = et >> 4, cck = et & 15;         // coalesced tile access: 16 threads per 256-byte row
         const int nsc = 2 * ng * RC_TILE;                // scale values per tile: [u | v][ng][128]
         float* su = sc;                                  // float32 scales of the current tile
@@ -230,36 +220,23 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
         issue_scales(blockIdx.x);
 
         uint32_t it = 0, tcount = 0;
-        RC_DECL(w_tfull); RC_DECL(w_bar); RC_DECL(w_wb);
-#ifdef ADE_PHASE_PROF
-        long long seg_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
-#ifdef ADE_PHASE_PROF
-        const long long tstart_ = clock64();
-#endif
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
             const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
             const int m = m0 + row;
             const bool live = m < p.M;
-#ifdef ADE_PHASE_PROF
-            const long long tp0_ = clock64();
-            long long lap_ = tp0_;
-#endif
             // base tile -> shared memory, two whole rows per warp instruction
             uint8_t* wbuf = wb_stage + (tcount & 1) * (RC_TILE * RC_WB_ROW);
             const uint32_t wbuf_s = smem_u32(wbuf);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int r_ = j * 16 + crow;
+            for (int j = 0; j < RC_TILE * 16 / RC_EPI_THREADS; ++j) {
+                const int r_ = j * (RC_EPI_THREADS / 16) + crow;
                 const bool lv = m0 + r_ < p.M;
                 cp_async16_zfill(wbuf_s + r_ * RC_WB_ROW + cck * 16,
                                  p.wb + static_cast<size_t>(lv ? m0 + r_ : 0) * p.N + n0 + cck * 8, lv);
             }
             cp_async_commit_group();
-            RC_LAP(0);
             // scales of this tile were copied during the previous one: convert them to float32
             cp_async_wait_group<1>();                    // all but the base tile just issued
-            RC_LAP(1);
             asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // copies visible, old scales unused
             for (int e = et; e < nsc; e += RC_EPI_THREADS) {
                 const int ee = e < ng * RC_TILE ? e : e - ng * RC_TILE;
@@ -267,37 +244,31 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 su[e] = bf16_bits_to_f32(e < ng * RC_TILE ? raw_u[i * ng + g] : raw_v[g * RC_TILE + i]);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // float32 scales complete
-            RC_LAP(2);
             issue_scales(tile + gridDim.x);              // next tile's scales, consumed one tile later
 
-            RC_LAP(3);
-#ifdef ADE_PHASE_PROF
-            w_bar += clock64() - tp0_;
-#endif
-            uint64_t acc[32];                            // 64 float32 accumulators as packed pairs
+            uint64_t acc[RC_CW / 2];                     // float32 accumulators as packed pairs
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            for (int i = 0; i < RC_CW / 2; ++i) acc[i] = 0ull;
             const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                { RC_T0(); wait_bounded(tfull0 + 8 * a, aph, abort_flag, p.status, 3); RC_ACC(w_tfull); }
+                wait_bounded(tfull0 + 8 * a, aph, abort_flag, p.status, 3);
                 tc_fence_after();
                 const float u = su[g * RC_TILE + row];
                 const uint64_t uu = f2_pack(u, u);
                 const uint32_t tbase = lane_addr + a * RC_TILE;
-                const ulonglong2* svp = reinterpret_cast<const ulonglong2*>(sv + g * RC_TILE + hh * 64);
-                uint32_t v[2][16];                       // two 16-column chunks in flight
-                tmem_ld16(tbase, v[0]);
+                const ulonglong2* svp = reinterpret_cast<const ulonglong2*>(sv + g * RC_TILE + hh * RC_CW);
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < RC_CW / 16; ++ch) {
+                    uint32_t vc[16];
+                    tmem_ld16(tbase + ch * 16, vc);
                     tmem_ld_wait();
-                    if (ch < 3) tmem_ld16(tbase + (ch + 1) * 16, v[(ch + 1) & 1]);
-                    if (ch == 3) {                       // accumulator stage is in registers: hand it back
+                    if (ch == RC_CW / 16 - 1) {          // accumulator stage is in registers: hand it back
                         tc_fence_before();
-                        mbar_arrive(tempty0 + 8 * a);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty0 + 8 * a);       // one arrival per warp
                     }
-                    const uint32_t (&vc)[16] = v[ch & 1];
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4) {
                         const ulonglong2 f = svp[ch * 4 + i4];            // column scales of 4 columns
@@ -308,39 +279,24 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                             const uint64_t pf = f2_add(f2_pack(__int_as_float(static_cast<int>(vc[i]) + 0x4B400000),
                                                                __int_as_float(static_cast<int>(vc[i + 1]) + 0x4B400000)),
                                                        neg_magic);
-#if defined(ADE_EXP) && ADE_EXP == 1
-                            acc[ch * 8 + i4 * 2 + j] ^= (static_cast<uint64_t>(vc[i]) << 32) | vc[i + 1];
-#elif defined(ADE_EXP) && ADE_EXP == 2
-                            acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], pf);
-#elif defined(ADE_EXP) && ADE_EXP == 3
-                            const uint64_t s2 = f2_mul(uu, j == 0 ? f.x : f.y);
-                            acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], f2_mul(pf, s2));
-#else
                             const uint64_t s2 = f2_mul(uu, j == 0 ? f.x : f.y);      // us * vs, exact
                             acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], f2_mul_rounded(pf, s2));
-#endif
                         }
                     }
                     if (DBG && live) {
-                        int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * 64 + ch * 16;
+                        int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * RC_CW + ch * 16;
 #pragma unroll
                         for (int i = 0; i < 16; i += 4)
                             *reinterpret_cast<int4*>(d + i) = make_int4(vc[i], vc[i + 1], vc[i + 2], vc[i + 3]);
                     }
                 }
             }
-#ifdef ADE_PHASE_PROF
-            const long long tf0_ = clock64();
-            lap_ = tf0_;
-#endif
             cp_async_wait_group<1>();                    // this thread's pieces of the base tile have landed
-            RC_LAP(4);
             asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // ... and everyone else's
-            RC_LAP(5);
             {
-                uint8_t* own = wbuf + row * RC_WB_ROW + hh * 128;          // this thread's row segment
+                uint8_t* own = wbuf + row * RC_WB_ROW + hh * (RC_CW * 2);  // this thread's row segment
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < RC_CW / 8; ++j) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(own + j * 16);
                     const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
                     uint32_t oq[4];
@@ -355,25 +311,16 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                     *reinterpret_cast<uint4*>(own + j * 16) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
                 }
             }
-            RC_LAP(6);
             asm volatile("bar.sync 1, %0;" ::"n"(RC_EPI_THREADS) : "memory");      // merged tile complete
-            RC_LAP(7);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int r_ = j * 16 + crow;
+            for (int j = 0; j < RC_TILE * 16 / RC_EPI_THREADS; ++j) {
+                const int r_ = j * (RC_EPI_THREADS / 16) + crow;
                 if (m0 + r_ < p.M)
                     *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(m0 + r_) * p.N + n0 + cck * 8) =
                         *reinterpret_cast<const uint4*>(wbuf + r_ * RC_WB_ROW + cck * 16);
             }
-#ifdef ADE_PHASE_PROF
-            w_wb += clock64() - tf0_;
-#endif
         }
-#ifdef ADE_PHASE_PROF
-        if (et == 0) { RC_PUT(0, w_tfull); RC_PUT(1, w_bar); RC_PUT(2, w_wb); RC_PUT(3, clock64() - tstart_);
-            for (int k = 0; k < 8; ++k) RC_PUT(8 + k, seg_[k]); }
-#endif
-    } else if (warp < 12) {
+    } else if (warp < RC_MMA_WARP) {
         // ------------------------------------------------------------------ unpack producers
         const int pt = threadIdx.x - RC_EPI_THREADS;
         const int c = pt & 3, rbase = pt >> 2;
@@ -417,9 +364,8 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
             cp_async_commit_group();                     // one group per item slot, empty past the end
         };
         for (int i = 0; i < RC_RAW_DEPTH - 1; ++i) issue(i);
-        RC_DECL(w_cp); RC_DECL(w_empty);
         for (int idx = 0; idx < total; ++idx) {
-            { RC_T0(); cp_async_wait_group<RC_RAW_DEPTH - 2>(); RC_ACC(w_cp); }     // item idx has landed
+            cp_async_wait_group<RC_RAW_DEPTH - 2>();     // item idx has landed
             const uint8_t* base = raw_ring + (idx % RC_RAW_DEPTH) * RC_RAW_ITEM;
             uint4 qa[4], qb[4];
             uint32_t za[4], zb[4];
@@ -439,7 +385,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
             advance(use);
             issue(idx + RC_RAW_DEPTH - 1);               // refill the slot consumed one iteration ago
             const uint32_t s = idx % RC_STAGES, ph = (idx / RC_STAGES) & 1;
-            { RC_T0(); wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 2); RC_ACC(w_empty); }
+            wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 2);
             uint8_t* A = stage_base + s * RC_STAGE_BYTES;
             uint8_t* B = A + RC_TILE * 128;
 #pragma unroll
@@ -448,23 +394,20 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 unpack_store(B, rbase + 32 * i, c, qb[i], zb[i]);
             }
             fence_proxy_async_smem();
-            mbar_arrive(full0 + 8 * s);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * s);   // one arrival per warp
         }
         cp_async_wait_group<0>();
-#ifdef ADE_PHASE_PROF
-        if (pt == 0) { RC_PUT(4, w_cp); RC_PUT(5, w_empty); }
-#endif
     } else {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t it = 0;
-            RC_DECL(w_full); RC_DECL(w_tempty);
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
                 for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t s = it % RC_STAGES, ph = (it / RC_STAGES) & 1;
                     const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                    { RC_T0(); wait_bounded(tempty0 + 8 * a, aph ^ 1, abort_flag, p.status, 4); RC_ACC(w_tempty); }
-                    { RC_T0(); wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1); RC_ACC(w_full); }
+                    wait_bounded(tempty0 + 8 * a, aph ^ 1, abort_flag, p.status, 4);
+                    wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + s * RC_STAGE_BYTES);
                     const uint64_t ad = smem_desc_k_sw128(sa);
@@ -476,14 +419,13 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                     tc_commit(tfull0 + 8 * a);           // accumulator stage ready
                 }
             }
-            RC_PUT(6, w_full); RC_PUT(7, w_tempty);
         }
         __syncwarp();
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 12) tmem_dealloc(tmem_base, RC_TMEM_COLS);
+    if (warp == RC_MMA_WARP) tmem_dealloc(tmem_base, RC_TMEM_COLS);
 }
 
 }  // namespace ade
