@@ -32,7 +32,8 @@ DEVICE_STATUS = {
 EXPORTS = (
     "ade_b200_device_status", "ade_b200_version", "ade_b200_last_cuda_error",
     "ade_b200_pack_codes", "ade_b200_pack_zeros",
-    "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored", "ade_b200_recon",
+    "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored",
+    "ade_b200_factored_static", "ade_b200_recon",
 )
 
 
@@ -73,6 +74,8 @@ def load() -> ctypes.CDLL:
     lib.ade_b200_factored_sync_offset.argtypes = [ci, ci]
     lib.ade_b200_factored_sync_offset.restype = sz
     lib.ade_b200_factored.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp, sz, ci, vp]
+    lib.ade_b200_factored_static.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, ci, vp]
+    lib.ade_b200_factored_static.restype = ci
     lib.ade_b200_recon.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp]
     for name in ("ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_factored", "ade_b200_recon"):
         getattr(lib, name).restype = ci

@@ -116,6 +116,12 @@ bool optin_factored() {
                                         static_cast<int>(ade::factored_smem_bytes(NT, 0))));
 }
 
+// ---- scratch of ade_b200_factored_static: lives in the library image, one copy per GPU that loads it.
+// Layout: 256 bytes holding the kernel's three sync words (always at the same place, whatever T and r),
+// then h = V^T x (bf16, T x r).  In host code this name is only a handle for cudaGetSymbolAddress.
+__device__ __align__(256) unsigned char g_static_scratch[ADE_B200_STATIC_SCRATCH_BYTES];
+void* g_static_scratch_addr[kMaxDevices] = {};
+
 }  // namespace
 
 extern "C" {
@@ -194,6 +200,60 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     p.rows_cap = (((d->M + grid - 1) / grid) + 31) / 32 * 32;
     if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (T <= 8) return launch_factored<1>(p, grid, st);
+    if (T <= 16) return launch_factored<2>(p, grid, st);
+    if (T <= 32) return launch_factored<4>(p, grid, st);
+    if (T <= 64) return launch_factored<8>(p, grid, st);
+    return launch_factored<16>(p, grid, st);
+}
+
+int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b, void* out,
+                             int T, void* stream) {
+    int rc = check_delta(d);
+    if (rc) return rc;
+    if (!d->vt || !x || !out) return ADE_ERR_NULL;
+    if ((y_dense == nullptr) == (w_b == nullptr)) return ADE_ERR_NULL;      // exactly one base term
+    if (T < 1 || T > ADE_B200_MAX_TOKENS) return ADE_ERR_SHAPE;
+    if (!aligned16(d->vt) || !aligned16(x) || !aligned16(out) || (y_dense && !aligned16(y_dense)) ||
+        (w_b && !aligned16(w_b)))
+        return ADE_ERR_ALIGN;
+    const size_t h_bytes = static_cast<size_t>(T) * d->r * sizeof(__nv_bfloat16);
+    if (256 + h_bytes > ADE_B200_STATIC_SCRATCH_BYTES) return ADE_ERR_SCRATCH;    // T * r beyond the built-in buffer
+    const DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc) return rc;
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return ADE_ERR_CUDA;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device (it is the current one): turn the symbol into a device address
+        void* addr = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&addr, g_static_scratch)) || addr == nullptr) return ADE_ERR_CUDA;
+        g_static_scratch_addr[dev] = addr;
+    }
+    char* base = static_cast<char*>(g_static_scratch_addr[dev]);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call left: the sync words must start at zero
+    if (!cuda_ok(cudaMemsetAsync(base, 0, 256, st))) return ADE_ERR_CUDA;
+    ade::FactoredParams p;
+    p.w_b = static_cast<const __nv_bfloat16*>(w_b);
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.y_dense = static_cast<const __nv_bfloat16*>(y_dense);
+    p.uq = d->uq;
+    p.vt = d->vt;
+    p.us = d->us;
+    p.uz = d->uz;
+    p.vs = d->vs;
+    p.vz = d->vz;
+    p.sync = reinterpret_cast<unsigned int*>(base);
+    p.h = reinterpret_cast<__nv_bfloat16*>(base + 256);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.T = T;
+    p.M = d->M;
+    p.N = d->N;
+    p.r = d->r;
+    const int grid = di->sms;
+    p.rows_cap = (((d->M + grid - 1) / grid) + 31) / 32 * 32;
+    if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
     if (T <= 8) return launch_factored<1>(p, grid, st);
     if (T <= 16) return launch_factored<2>(p, grid, st);
     if (T <= 32) return launch_factored<4>(p, grid, st);

@@ -120,6 +120,29 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
                       void* out, void* scratch, size_t scratch_bytes, int T, void* stream);
 
 /*
+ * Factored application without a caller-supplied scratch buffer.  No counterpart in the reference.
+ *
+ * Same arithmetic, arguments and requirements as ade_b200_factored, but h = V^T x and the kernel's sync
+ * words live in a fixed array inside the library (ADE_B200_STATIC_SCRATCH_BYTES of device memory, held by
+ * every GPU that loads the library until the process exits).  It is meant for callers that must not
+ * allocate device memory at the point of the call and have no buffer of their own to lend: code that
+ * runs inside another framework's memory plan, under a fixed memory budget, or in a context where
+ * cudaMalloc's implicit device synchronisation is not acceptable.  The entry point calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *   Limit: 256 + 2 * T * r <= ADE_B200_STATIC_SCRATCH_BYTES (T * r <= 131072, e.g. T = 128 at r = 1024);
+ *   larger products return ADE_ERR_SCRATCH.
+ *   The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
+ *   current); make that first call outside any stream capture.
+ *   All calls on a device share the one array, and it keeps the previous call's contents; every call
+ *   clears the sync words on `stream` before its launch.  Two calls that overlap on the GPU (different
+ *   streams without ordering) race on h and on the sync words: serialise them, or use ade_b200_factored
+ *   with one buffer per stream.
+ */
+#define ADE_B200_STATIC_SCRATCH_BYTES 262400
+int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b,
+                             void* out, int T, void* stream);
+
+/*
  * Reconstructed application (replaces ade_recon_int4, src/kernels.py:383-397):
  *
  *     w_out[m][n] = bf16( float(w_b[m][n]) + sum_g (us[m][g] * vs[g][n]) * float(P_g[m][n]) )
