@@ -118,6 +118,7 @@ def cpu_sample(rows, steps, warmup, seed=0):
     from ade_b200 import synth
     from oracle import oracle as O
 
+    O.use_all_cores()
     _, M, N = MODULES[0]
     tp = synth.random_packed(M, N, RANK, seed)
     p = O.packed_from_torch(tp)

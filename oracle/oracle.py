@@ -181,6 +181,20 @@ def threads() -> int:
     return int(lib().ade_oracle_threads())
 
 
+def use_all_cores() -> int:
+    """Let the C oracle and numpy's BLAS use every host core, whatever OMP_NUM_THREADS the launcher
+    exported; returns the thread count of the C oracle."""
+    n = os.cpu_count() or 1
+    lib().ade_oracle_set_threads(n)
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    return threads()
+
+
 def group_product(p: dict, g: int, G: int = 128, rows=None) -> np.ndarray:
     """INT32 ``prod`` of group g for rows [m0, m1) (default all): src/quantization.py:309-312."""
     M, N, r, ng = _dims(p, G)
