@@ -96,6 +96,19 @@ __global__ void pack_zeros_kernel(const uint16_t* __restrict__ z, uint8_t* __res
         out[i] = static_cast<uint8_t>(static_cast<int>(ade::bf16_bits_to_f32(z[i])));
 }
 
+// Rows per CTA: even split, minus `unit_rows` for each of the last CTAs that also computes 16 ranks of
+// h = V^T x first.  That unit reads only about 5.5 rows' worth of bytes, but it costs one memory round trip
+// under full load (4-5 us measured on 4096- and 11008-wide modules) before its own stream of W_b even
+// starts; 14 rows is the compromise that helped every measured shape (a larger discount starves the
+// other CTAs when many units exist, r = 512 has 32 of them).
+void set_row_split(ade::FactoredParams& p, int grid) {
+    const int n_units = p.r / 16;
+    const int unit_ctas = n_units < grid ? n_units : grid;
+    p.unit_rows = (p.w_b != nullptr && p.M / grid >= 24) ? 14 : 0;
+    const long long budget = static_cast<long long>(p.M) + static_cast<long long>(unit_ctas) * p.unit_rows;
+    p.rows_cap = static_cast<int>(((budget + grid - 1) / grid + 1 + 31) / 32 * 32);
+}
+
 template <int NT, bool FUSE>
 int launch_factored_one(const ade::FactoredParams& p, int grid, cudaStream_t st) {
     const size_t smem = ade::factored_smem_bytes(NT, FUSE ? p.rows_cap : 0);
@@ -197,7 +210,7 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     p.N = d->N;
     p.r = d->r;
     const int grid = di->sms;                                   // one persistent CTA per SM, all co-resident
-    p.rows_cap = (((d->M + grid - 1) / grid) + 31) / 32 * 32;
+    set_row_split(p, grid);
     if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (T <= 8) return launch_factored<1>(p, grid, st);
@@ -252,7 +265,7 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     p.N = d->N;
     p.r = d->r;
     const int grid = di->sms;
-    p.rows_cap = (((d->M + grid - 1) / grid) + 31) / 32 * 32;
+    set_row_split(p, grid);
     if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
     if (T <= 8) return launch_factored<1>(p, grid, st);
     if (T <= 16) return launch_factored<2>(p, grid, st);

@@ -50,6 +50,7 @@ struct FactoredParams {
     __nv_bfloat16* out;            // [T][M]
     int T, M, N, r;
     int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
+    int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
 };
 
 __host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap) {
@@ -114,6 +115,36 @@ __device__ __forceinline__ void zero_acc(float (&acc)[2][NT][4]) {
 // phase A: h for the 16 ranks k0 .. k0+15; the d_i axis is split over the warps in chunks of 128.
 // ---------------------------------------------------------------------------------------------
 template <int NT>
+struct XvRegs {
+    uint4 q0, q1;              // 32 codes of ranks gid and gid + 8
+    uint4 s[4];                // 32 bf16 scales of the thread's columns
+    uint4 z[2];                // 32 zero-points
+    uint4 x[NT <= 2 ? NT : 1][4];   // activations of the thread's columns (prefetched only for small T)
+};
+
+template <int NT>
+__device__ __forceinline__ void xv_load(XvRegs<NT>& R, const FactoredParams& p, const uint8_t* row0,
+                                        const uint8_t* row1, int g, int nb, int gid) {
+    const int N = p.N;
+    R.q0 = ldg16_stream(row0 + (nb >> 1));
+    R.q1 = ldg16_stream(row1 + (nb >> 1));
+    const uint16_t* sp = p.vs + static_cast<size_t>(g) * N + nb;
+    const uint8_t* zp = p.vz + static_cast<size_t>(g) * N + nb;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) R.s[j] = ldg16(sp + 8 * j);
+    R.z[0] = ldg16(zp);
+    R.z[1] = ldg16(zp + 16);
+    if (NT <= 2) {
+#pragma unroll
+        for (int nt = 0; nt < (NT <= 2 ? NT : 1); ++nt) {
+            const int tok = min(nt * 8 + gid, p.T - 1);
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) R.x[nt][wi] = ldg16(p.x + static_cast<size_t>(tok) * N + nb + 8 * wi);
+        }
+    }
+}
+
+template <int NT>
 __device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32][33], int k0, int warp, int gid,
                                         int tig) {
     const int N = p.N, T = p.T;
@@ -124,19 +155,16 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32
     float acc[2][NT][4];             // only [0] is used; [1] stays zero so that the shared reducer applies
     zero_acc<NT>(acc);
     const int nchunks = N >> 7;
+    XvRegs<NT> cur, nxt;             // one chunk in flight while the previous one is multiplied
+    if (warp < nchunks) xv_load<NT>(cur, p, row0, row1, g, (warp << 7) + tig * 32, gid);
     for (int c = warp; c < nchunks; c += FA_WARPS) {
         const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
-        const uint4 q0 = ldg16_stream(row0 + (nb >> 1));
-        const uint4 q1 = ldg16_stream(row1 + (nb >> 1));
-        const uint16_t* sp = p.vs + static_cast<size_t>(g) * N + nb;
-        const uint8_t* zp = p.vz + static_cast<size_t>(g) * N + nb;
-        const uint4 s0 = ldg16(sp), s1 = ldg16(sp + 8), s2 = ldg16(sp + 16), s3 = ldg16(sp + 24);
-        const uint4 z0 = ldg16(zp), z1 = ldg16(zp + 16);
-        const uint32_t cw0[4] = {q0.x, q0.y, q0.z, q0.w};
-        const uint32_t cw1[4] = {q1.x, q1.y, q1.z, q1.w};
-        const uint32_t sw[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w,
-                                 s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
-        const uint32_t zw[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+        if (c + FA_WARPS < nchunks) xv_load<NT>(nxt, p, row0, row1, g, ((c + FA_WARPS) << 7) + tig * 32, gid);
+        const uint32_t cw0[4] = {cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w};
+        const uint32_t cw1[4] = {cur.q1.x, cur.q1.y, cur.q1.z, cur.q1.w};
+        const uint32_t sw[16] = {cur.s[0].x, cur.s[0].y, cur.s[0].z, cur.s[0].w, cur.s[1].x, cur.s[1].y, cur.s[1].z, cur.s[1].w,
+                                 cur.s[2].x, cur.s[2].y, cur.s[2].z, cur.s[2].w, cur.s[3].x, cur.s[3].y, cur.s[3].z, cur.s[3].w};
+        const uint32_t zw[8] = {cur.z[0].x, cur.z[0].y, cur.z[0].z, cur.z[0].w, cur.z[1].x, cur.z[1].y, cur.z[1].z, cur.z[1].w};
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {                  // 8 columns per packed word
             uint32_t e0[4], e1[4], a0[4], a1[4];
@@ -154,12 +182,15 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int tok = nt * 8 + gid;
-                uint4 xq = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < T) xq = ldg16(p.x + static_cast<size_t>(tok) * N + nb + 8 * wi);
+                uint4 xq;
+                if (NT <= 2) xq = cur.x[NT <= 2 ? nt : 0][wi];
+                else xq = ldg16(p.x + static_cast<size_t>(min(tok, T - 1)) * N + nb + 8 * wi);
+                if (tok >= T) xq = make_uint4(0u, 0u, 0u, 0u);
                 mma_bf16(acc[0][nt], a0[0], a1[0], a0[1], a1[1], xq.x, xq.y);
                 mma_bf16(acc[0][nt], a0[2], a1[2], a0[3], a1[3], xq.z, xq.w);
             }
         }
+        if (c + FA_WARPS < nchunks) cur = nxt;
     }
     __nv_bfloat16* h = p.h;
     const int r = p.r;
@@ -303,6 +334,17 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
     }
 }
 
+// First row of CTA c's slice.  The last `unit_ctas` CTAs own a phase-A unit each and give up
+// `unit_rows` rows for it; the rows are otherwise split evenly.
+__device__ __forceinline__ int slice_start(int c, int G, int M, int unit_ctas, int unit_rows) {
+    if (c >= G) return M;
+    const long long budget = static_cast<long long>(M) + static_cast<long long>(unit_ctas) * unit_rows;
+    long long s = budget * c / G;
+    const int first = G - unit_ctas;
+    if (c > first) s -= static_cast<long long>(c - first) * unit_rows;
+    return static_cast<int>(s < 0 ? 0 : (s > M ? M : s));
+}
+
 template <int NT, bool FUSE_WB>
 __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredParams p) {
     extern __shared__ float fsmem[];
@@ -311,9 +353,10 @@ __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredPara
     float* ybuf = fsmem + FA_WARPS * 32 * 33;              // [rows_cap][YS]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int G = gridDim.x, c = blockIdx.x;
-    const int row0 = static_cast<int>(static_cast<long long>(p.M) * c / G);
-    const int row1 = static_cast<int>(static_cast<long long>(p.M) * (c + 1) / G);
     const int n_units = p.r >> 4;
+    const int unit_ctas = min(n_units, G);
+    const int row0 = slice_start(c, G, p.M, unit_ctas, p.unit_rows);
+    const int row1 = slice_start(c + 1, G, p.M, unit_ctas, p.unit_rows);
 
     // ---- phase A: units are dealt from the last CTA backwards (those CTAs own the fewest rows)
     {
@@ -336,7 +379,7 @@ __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredPara
         for (int blk = row0; blk < row1; blk += FA_ROWS) {
             float acc[2][NT][4];
             zero_acc<NT>(acc);
-            constexpr int DEPTH = NT <= 2 ? 3 : 2;
+            constexpr int DEPTH = NT == 1 ? 4 : (NT == 2 ? 3 : 2);
             wx_block<NT, DEPTH, (NT <= 4)>(p, acc, blk, row1, warp, gid, tig);
             float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
             reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) { yb[row * YS + t] = s; });
