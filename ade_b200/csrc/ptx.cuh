@@ -108,6 +108,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// store the same 32-bit value into 32 lanes x 16 consecutive columns of tensor memory.  The store takes a
+// run of consecutive registers, so it is issued four columns at a time from four registers that hold
+// the value for the whole kernel, instead of tying up sixteen.
+__device__ __forceinline__ void tmem_st16_fill(uint32_t taddr, const uint32_t (&v)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr + 4 * i), "r"(v[0]),
+                     "r"(v[1]), "r"(v[2]), "r"(v[3])
+                     : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

@@ -44,6 +44,10 @@ constexpr int RC_RAW_ITEM = RC_PROD_THREADS * (8 * 16 + 8 * 4);   // per item: 8
 constexpr long long RC_SPIN_LIMIT = 2000000000LL;       // clock cycles (about one second)
 // instruction descriptor: D = S32 (bits 4-5 = 2), A = B = signed 8-bit (bits 7-9, 10-12 = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 = 16 (bits 17-22), M >> 4 = 8 (bits 24-28)
+// Every INT32 accumulator starts a group at the bit pattern of the float 1.5 * 2^23, so that after the
+// integer MMAs its bits read as the float 1.5 * 2^23 + P (exact for |P| < 2^22; here |P| <= 28 800) and the
+// int -> float conversion is one float subtraction.
+constexpr uint32_t RC_MAGIC = 0x4B400000u;
 constexpr uint32_t RC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);
 
 struct ReconParams {
@@ -218,6 +222,20 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
             cp_async_commit_group();
         };
         issue_scales(blockIdx.x);
+        uint32_t magic4[4];                          // kept in four distinct registers (asm volatile: not merged)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(magic4[i]) : "n"(RC_MAGIC));
+#pragma unroll
+        for (int st = 0; st < 2; ++st)
+#pragma unroll
+            for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_st16_fill(lane_addr + st * RC_TILE + ch * 16, magic4);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {                             // both accumulator stages start out armed and free
+            mbar_arrive(tempty0);
+            mbar_arrive(tempty0 + 8);
+        }
 
         uint32_t it = 0, tcount = 0;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
@@ -259,26 +277,29 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 const uint64_t uu = f2_pack(u, u);
                 const uint32_t tbase = lane_addr + a * RC_TILE;
                 const ulonglong2* svp = reinterpret_cast<const ulonglong2*>(sv + g * RC_TILE + hh * RC_CW);
+                // all of this thread's columns of the group in one go: both loads in flight together, then the
+                // columns are re-armed and the accumulator stage is handed back before any arithmetic
+                uint32_t v[RC_CW / 16][16];
+#pragma unroll
+                for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_ld16(tbase + ch * 16, v[ch]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * a);               // one arrival per warp
 #pragma unroll
                 for (int ch = 0; ch < RC_CW / 16; ++ch) {
-                    uint32_t vc[16];
-                    tmem_ld16(tbase + ch * 16, vc);
-                    tmem_ld_wait();
-                    if (ch == RC_CW / 16 - 1) {          // accumulator stage is in registers: hand it back
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty0 + 8 * a);       // one arrival per warp
-                    }
+                    const uint32_t (&vc)[16] = v[ch];
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4) {
                         const ulonglong2 f = svp[ch * 4 + i4];            // column scales of 4 columns
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const int i = i4 * 4 + j * 2;
-                            // exact int -> float for |P| < 2^22: 1.5 * 2^23 + P has P in its mantissa
-                            const uint64_t pf = f2_add(f2_pack(__int_as_float(static_cast<int>(vc[i]) + 0x4B400000),
-                                                               __int_as_float(static_cast<int>(vc[i + 1]) + 0x4B400000)),
-                                                       neg_magic);
+                            // the accumulator started at RC_MAGIC: its bits are the float 1.5 * 2^23 + P, exactly
+                            const uint64_t pf = f2_add(f2_pack(__uint_as_float(vc[i]), __uint_as_float(vc[i + 1])), neg_magic);
                             const uint64_t s2 = f2_mul(uu, j == 0 ? f.x : f.y);      // us * vs, exact
                             acc[ch * 8 + i4 * 2 + j] = f2_add(acc[ch * 8 + i4 * 2 + j], f2_mul_rounded(pf, s2));
                         }
@@ -287,7 +308,8 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                         int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * RC_CW + ch * 16;
 #pragma unroll
                         for (int i = 0; i < 16; i += 4)
-                            *reinterpret_cast<int4*>(d + i) = make_int4(vc[i], vc[i + 1], vc[i + 2], vc[i + 3]);
+                            *reinterpret_cast<int4*>(d + i) = make_int4(vc[i] - RC_MAGIC, vc[i + 1] - RC_MAGIC, vc[i + 2] - RC_MAGIC,
+                                                                        vc[i + 3] - RC_MAGIC);
                     }
                 }
             }
@@ -406,7 +428,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t s = it % RC_STAGES, ph = (it / RC_STAGES) & 1;
                     const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                    wait_bounded(tempty0 + 8 * a, aph ^ 1, abort_flag, p.status, 4);
+                    wait_bounded(tempty0 + 8 * a, aph, abort_flag, p.status, 4);   // use u of a stage waits for its u-th release
                     wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + s * RC_STAGE_BYTES);
@@ -414,7 +436,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                     const uint64_t bd = smem_desc_k_sw128(sa + RC_TILE * 128);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)          // 32 bytes of K per MMA inside the 128-byte row
-                        tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * k, bd + 2 * k, RC_IDESC, k > 0 ? 1u : 0u);
+                        tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * k, bd + 2 * k, RC_IDESC, 1u);   // always on top of RC_MAGIC
                     tc_commit(empty0 + 8 * s);           // operand stage reusable once these MMAs retire
                     tc_commit(tfull0 + 8 * a);           // accumulator stage ready
                 }
