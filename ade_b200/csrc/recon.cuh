@@ -78,6 +78,7 @@ __device__ __forceinline__ void wait_bounded(uint32_t bar, uint32_t parity, vola
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(64);                                  // leave the issue slots to the warps that have work
         if (*abort_flag) return;
         if (clock64() - t0 > RC_SPIN_LIMIT) {
             *abort_flag = 1;
