@@ -104,15 +104,15 @@ __global__ void pack_zeros_kernel(const uint16_t* __restrict__ z, uint8_t* __res
 void set_row_split(ade::FactoredParams& p, int grid) {
     const int n_units = p.r / 16;
     const int unit_ctas = n_units < grid ? n_units : grid;
-    p.unit_rows = (p.w_b != nullptr && p.M / grid >= 24) ? 14 : 0;
+    p.unit_rows = (p.w_b != nullptr && p.M / grid >= 24 && p.T > 16) ? 14 : 0;   // side warps hide the unit at T <= 16
     const long long budget = static_cast<long long>(p.M) + static_cast<long long>(unit_ctas) * p.unit_rows;
     p.rows_cap = static_cast<int>(((budget + grid - 1) / grid + 1 + 31) / 32 * 32);
 }
 
 template <int NT, bool FUSE>
 int launch_factored_one(const ade::FactoredParams& p, int grid, cudaStream_t st) {
-    const size_t smem = ade::factored_smem_bytes(NT, FUSE ? p.rows_cap : 0);
-    ade::factored_kernel<NT, FUSE><<<grid, ade::FA_THREADS, smem, st>>>(p);
+    const size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
+    ade::factored_kernel<NT, FUSE><<<grid, ade::fa_threads(NT), smem, st>>>(p);
     return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
 
@@ -123,10 +123,10 @@ int launch_factored(const ade::FactoredParams& p, int grid, cudaStream_t st) {
 
 template <int NT>
 bool optin_factored() {
-    const int smem = static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap));
+    const int smem = static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, NT <= 2 ? 16 : 0, ADE_B200_MAX_RANK));
     return cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) &&
            cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(ade::factored_smem_bytes(NT, 0))));
+                                        static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, NT <= 2 ? 16 : 0, ADE_B200_MAX_RANK))));
 }
 
 // ---- scratch of ade_b200_factored_static: lives in the library image, one copy per GPU that loads it.
@@ -169,7 +169,8 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
 
 size_t ade_b200_factored_scratch_bytes(int T, int r) {
     if (T < 1 || r < 1) return 0;
-    const size_t b = static_cast<size_t>(T) * r * sizeof(__nv_bfloat16);
+    // h: bf16 [T][r]; for T <= 16 two float32 partial sums [2][T][r] (each half of d_i is summed by another CTA)
+    const size_t b = static_cast<size_t>(T) * r * (T <= 16 ? 2 * sizeof(float) : sizeof(__nv_bfloat16));
     return ((b + 255) & ~static_cast<size_t>(255)) + 256;          // h, then the three sync words
 }
 
@@ -230,7 +231,7 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     if (!aligned16(d->vt) || !aligned16(x) || !aligned16(out) || (y_dense && !aligned16(y_dense)) ||
         (w_b && !aligned16(w_b)))
         return ADE_ERR_ALIGN;
-    const size_t h_bytes = static_cast<size_t>(T) * d->r * sizeof(__nv_bfloat16);
+    const size_t h_bytes = static_cast<size_t>(T) * d->r * (T <= 16 ? 2 * sizeof(float) : sizeof(__nv_bfloat16));
     if (256 + h_bytes > ADE_B200_STATIC_SCRATCH_BYTES) return ADE_ERR_SCRATCH;    // T * r beyond the built-in buffer
     const DeviceInfo* di = nullptr;
     rc = device_info(&di);

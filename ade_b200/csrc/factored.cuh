@@ -10,9 +10,12 @@
 //   wait                   until the counter shows that every h unit has been written (bounded spin);
 //   phase U  (all CTAs)    out[t][m] = y[t][m] + sum_g us[m][g] * sum_{k in g} (Ucode[m][k] - uz[m][g]) * h[t][k].
 //
-// Phase A is 3 % of the bytes and finishes long before phase W does, so the grid-wide dependency
-// h -> phase U costs no idle time.  Rows are split evenly over the CTAs (to within one row), so
-// every SM streams the same number of bytes of W_b.
+// Phase A is 3 % of the bytes but a full memory round trip under load.  For T <= 16 four extra warps
+// per CTA run it next to the eight that stream W_b (a unit is then 16 ranks x half of d_i, written as a
+// float32 partial sum; the halves are added and rounded to bf16 once per CTA, into shared memory, before
+// phase U), so the grid-wide dependency h -> phase U costs no idle time.  For larger T the main warps
+// run phase A first and the CTAs that own a unit get fewer rows.  Rows are otherwise split evenly over
+// the CTAs (to within one row), so every SM streams the same number of bytes of W_b.
 //
 // All three phases are weight-streaming skinny GEMMs: the weights (bf16 rows of W_b, or 4-bit codes)
 // are the 16-row operand of a warp MMA and come straight from global memory with 128-bit loads, a
@@ -31,6 +34,13 @@ namespace ade {
 
 constexpr int FA_WARPS = 8;
 constexpr int FA_THREADS = FA_WARPS * 32;
+constexpr int FA_SIDE_WARPS = 4;               // extra warps that compute h = V^T x next to the W_b stream (T <= 16)
+__host__ __device__ constexpr bool fa_side(int NT) { return NT <= 2; }
+__host__ __device__ constexpr int fa_threads(int NT) { return FA_THREADS + (fa_side(NT) ? FA_SIDE_WARPS * 32 : 0); }
+
+// barrier among the 8 main warps only (the side warps never join it)
+__device__ __forceinline__ void main_sync() { asm volatile("bar.sync 1, %0;" ::"n"(FA_THREADS) : "memory"); }
+__device__ __forceinline__ void side_sync() { asm volatile("bar.sync 2, %0;" ::"n"(FA_SIDE_WARPS * 32) : "memory"); }
 constexpr int FA_ROWS = 32;                    // output rows per pass (two m16 tiles per warp)
 constexpr uint32_t kBf2_128 = 0x43004300u;     // bf16x2 (128, 128)
 constexpr long long FA_SPIN_LIMIT = 2000000000LL;   // clock cycles (about one second)
@@ -45,7 +55,7 @@ struct FactoredParams {
     const uint8_t* uz;             // [M][ng]
     const uint16_t* vs;            // [ng][N]
     const uint8_t* vz;             // [ng][N]
-    __nv_bfloat16* h;              // scratch [T][r]
+    __nv_bfloat16* h;              // scratch: bf16 [T][r], or float32 [2][T][r] partial sums when T <= 16
     unsigned int* sync;            // scratch: [0] units arrived, [1] CTAs done, [2] status (0 = ok)
     __nv_bfloat16* out;            // [T][M]
     int T, M, N, r;
@@ -53,8 +63,10 @@ struct FactoredParams {
     int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
 };
 
-__host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap) {
-    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + static_cast<size_t>(rows_cap) * (8 * NT + 1)) * sizeof(float);
+__host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap, int T, int r) {
+    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + (fa_side(NT) ? FA_SIDE_WARPS * 32 * 17 : 0) +
+            static_cast<size_t>(rows_cap) * (8 * NT + 1)) * sizeof(float) +
+           (fa_side(NT) ? static_cast<size_t>(T) * (r + 8) * 2 + 16 : 0);
 }
 
 // one packed word (8 codes) -> 4 bf16x2 registers holding 128 + code, codes in natural order
@@ -85,7 +97,7 @@ __device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (
                 }
             }
         }
-        __syncthreads();
+        main_sync();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int e = threadIdx.x + i * FA_THREADS;
@@ -97,7 +109,7 @@ __device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (
                 sink(row, b * 32 + tok, s);
             }
         }
-        __syncthreads();
+        main_sync();
     }
 }
 
@@ -144,9 +156,11 @@ __device__ __forceinline__ void xv_load(XvRegs<NT>& R, const FactoredParams& p, 
     }
 }
 
-template <int NT>
-__device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32][33], int k0, int warp, int gid,
-                                        int tig) {
+// TEAM warps (the CTA's 8 main warps, or its 4 side warps) split the d_i axis in chunks of 128 columns.
+// Chunks [c_begin, c_end) only; the sum goes to hf (float32 partial, [T][r]) when given, else to p.h as bf16.
+template <int NT, int TEAM>
+__device__ __forceinline__ void xv_unit(const FactoredParams& p, float* redbuf, int k0, int c_begin, int c_end,
+                                        float* hf, int warp, int gid, int tig) {
     const int N = p.N, T = p.T;
     const int g = k0 >> 7;
     const size_t rowb = static_cast<size_t>(N >> 1);
@@ -154,12 +168,12 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32
     const uint8_t* row1 = row0 + 8 * rowb;
     float acc[2][NT][4];             // only [0] is used; [1] stays zero so that the shared reducer applies
     zero_acc<NT>(acc);
-    const int nchunks = N >> 7;
+    const int nchunks = c_end;
     XvRegs<NT> cur, nxt;             // one chunk in flight while the previous one is multiplied
-    if (warp < nchunks) xv_load<NT>(cur, p, row0, row1, g, (warp << 7) + tig * 32, gid);
-    for (int c = warp; c < nchunks; c += FA_WARPS) {
+    if (c_begin + warp < nchunks) xv_load<NT>(cur, p, row0, row1, g, ((c_begin + warp) << 7) + tig * 32, gid);
+    for (int c = c_begin + warp; c < nchunks; c += TEAM) {
         const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
-        if (c + FA_WARPS < nchunks) xv_load<NT>(nxt, p, row0, row1, g, ((c + FA_WARPS) << 7) + tig * 32, gid);
+        if (c + TEAM < nchunks) xv_load<NT>(nxt, p, row0, row1, g, ((c + TEAM) << 7) + tig * 32, gid);
         const uint32_t cw0[4] = {cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w};
         const uint32_t cw1[4] = {cur.q1.x, cur.q1.y, cur.q1.z, cur.q1.w};
         const uint32_t sw[16] = {cur.s[0].x, cur.s[0].y, cur.s[0].z, cur.s[0].w, cur.s[1].x, cur.s[1].y, cur.s[1].z, cur.s[1].w,
@@ -190,13 +204,37 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float (*red)[32
                 mma_bf16(acc[0][nt], a0[2], a1[2], a0[3], a1[3], xq.z, xq.w);
             }
         }
-        if (c + FA_WARPS < nchunks) cur = nxt;
+        if (c + TEAM < nchunks) cur = nxt;
     }
-    __nv_bfloat16* h = p.h;
-    const int r = p.r;
-    reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) {
-        if (row < 16 && t < T) h[static_cast<size_t>(t) * r + k0 + row] = __float2bfloat16_rn(s);
-    });
+    // fixed-order sum over the team, 32 tokens at a time: redbuf[TEAM][32 tokens][16 ranks (+1 pad)]
+    float (*red)[32][17] = reinterpret_cast<float (*)[32][17]>(redbuf);
+    const int tl = (TEAM == FA_WARPS ? threadIdx.x : threadIdx.x - FA_THREADS);      // index inside the team
+#pragma unroll
+    for (int b = 0; b < (NT + 3) / 4; ++b) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nt = b * 4 + j;
+            if (nt < NT) {
+                red[warp][j * 8 + 2 * tig][gid] = acc[0][nt][0];
+                red[warp][j * 8 + 2 * tig + 1][gid] = acc[0][nt][1];
+                red[warp][j * 8 + 2 * tig][gid + 8] = acc[0][nt][2];
+                red[warp][j * 8 + 2 * tig + 1][gid + 8] = acc[0][nt][3];
+            }
+        }
+        if (TEAM == FA_WARPS) main_sync(); else side_sync();
+        for (int e = tl; e < 16 * 32; e += TEAM * 32) {
+            const int rank = e & 15, tok = e >> 4;
+            const int t = b * 32 + tok;
+            if (tok < 8 * (NT - 4 * b) && t < T) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < TEAM; ++w) sum += red[w][tok][rank];
+                if (hf) hf[static_cast<size_t>(t) * p.r + k0 + rank] = sum;
+                else p.h[static_cast<size_t>(t) * p.r + k0 + rank] = __float2bfloat16_rn(sum);
+            }
+        }
+        if (TEAM == FA_WARPS) main_sync(); else side_sync();
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -275,9 +313,10 @@ __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2
 // ---------------------------------------------------------------------------------------------
 // phase U: acc += sum_g us * (Ucode - uz)[rows, group g] h^T, one rank group per warp iteration.
 // ---------------------------------------------------------------------------------------------
-template <int NT>
+// SPLIT: h has been staged in shared memory (hs, bf16 [T][r + 8]); otherwise it is read from p.h (L2).
+template <int NT, bool SPLIT>
 __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
-                                         int warp, int gid, int tig) {
+                                         const __nv_bfloat16* hs, int warp, int gid, int tig) {
     const int T = p.T, r = p.r;
     const int ng = r >> 7;
     const size_t rowb = static_cast<size_t>(r >> 1);
@@ -314,7 +353,10 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 uint4 hq = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < T) hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
+                if (tok < T) {
+                    if (SPLIT) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
+                    else hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
+                }
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
                     mma_bf16(pa[mt], a[mt][0][4 * wi], a[mt][1][4 * wi], a[mt][0][4 * wi + 1], a[mt][1][4 * wi + 1],
@@ -346,31 +388,47 @@ __device__ __forceinline__ int slice_start(int c, int G, int M, int unit_ctas, i
 }
 
 template <int NT, bool FUSE_WB>
-__global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredParams p) {
+__global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const FactoredParams p) {
     extern __shared__ float fsmem[];
     float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(fsmem);
     constexpr int YS = 8 * NT + 1;                         // padded row stride of the y buffer
-    float* ybuf = fsmem + FA_WARPS * 32 * 33;              // [rows_cap][YS]
+    constexpr bool SIDE = fa_side(NT);
+    float* side_red = fsmem + FA_WARPS * 32 * 33;          // [4][32][17]
+    float* ybuf = side_red + (SIDE ? FA_SIDE_WARPS * 32 * 17 : 0);     // [rows_cap][YS]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int G = gridDim.x, c = blockIdx.x;
-    const int n_units = p.r >> 4;
+    const int n_units = (p.r >> 4) * (SIDE ? 2 : 1);       // with side warps a unit is 16 ranks x half of d_i
     const int unit_ctas = min(n_units, G);
+    const int nchunks = p.N >> 7;
     const int row0 = slice_start(c, G, p.M, unit_ctas, p.unit_rows);
     const int row1 = slice_start(c + 1, G, p.M, unit_ctas, p.unit_rows);
 
-    // ---- phase A: units are dealt from the last CTA backwards (those CTAs own the fewest rows)
-    {
+    // ---- phase A: units are dealt from the last CTA backwards.  With side warps (T <= 16) they do it
+    // while the main warps are already streaming W_b, and leave; otherwise the main warps do it first.
+    if (SIDE && warp >= FA_WARPS) {
         unsigned int done = 0;
         for (int u = G - 1 - c; u < n_units; u += G) {
-            xv_unit<NT>(p, red, u * 16, warp, gid, tig);
+            const int half = u & 1, mid = (nchunks + 1) >> 1;
+            xv_unit<NT, FA_SIDE_WARPS>(p, side_red, (u >> 1) * 16, half ? mid : 0, half ? nchunks : mid,
+                                       reinterpret_cast<float*>(p.h) + static_cast<size_t>(half) * p.T * p.r,
+                                       warp - FA_WARPS, gid, tig);
             ++done;
         }
-        if (done) {                                        // uniform per CTA
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                __threadfence();
-                atomicAdd(p.sync, done);
-            }
+        if (done && threadIdx.x == FA_THREADS) {           // xv_unit ended with a barrier of the side warps
+            __threadfence();
+            atomicAdd(p.sync, done);
+        }
+        return;
+    }
+    if (!SIDE) {
+        unsigned int done = 0;
+        for (int u = G - 1 - c; u < n_units; u += G) {
+            xv_unit<NT, FA_WARPS>(p, fsmem, u * 16, 0, nchunks, nullptr, warp, gid, tig);
+            ++done;
+        }
+        if (done && threadIdx.x == 0) {                    // xv_unit ended with a barrier of the main warps
+            __threadfence();
+            atomicAdd(p.sync, done);
         }
     }
 
@@ -379,7 +437,7 @@ __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredPara
         for (int blk = row0; blk < row1; blk += FA_ROWS) {
             float acc[2][NT][4];
             zero_acc<NT>(acc);
-            constexpr int DEPTH = NT == 1 ? 4 : (NT == 2 ? 3 : 2);
+            constexpr int DEPTH = NT == 1 ? 3 : 2;
             wx_block<NT, DEPTH, (NT <= 4)>(p, acc, blk, row1, warp, gid, tig);
             float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
             reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) { yb[row * YS + t] = s; });
@@ -396,13 +454,33 @@ __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredPara
             }
         }
     }
-    __syncthreads();
+    main_sync();
+    __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(ybuf + static_cast<size_t>(p.rows_cap) * YS);   // [T][r + 8]
+    if (SIDE) {
+        // the two float32 halves of h, summed, rounded to bf16 once and kept in shared memory for phase U
+        const float* h0 = reinterpret_cast<const float*>(p.h);
+        const float* h1 = h0 + static_cast<size_t>(p.T) * p.r;
+        const int quads = (p.T * p.r) >> 2;
+        for (int i = threadIdx.x; i < quads; i += FA_THREADS) {
+            const uint4 a = ldcg16(h0 + 4 * i), b = ldcg16(h1 + 4 * i);
+            const int t = (4 * i) / p.r, k = (4 * i) % p.r;
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(__uint_as_float(a.x) + __uint_as_float(b.x),
+                                                            __uint_as_float(a.y) + __uint_as_float(b.y));
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(__uint_as_float(a.z) + __uint_as_float(b.z),
+                                                            __uint_as_float(a.w) + __uint_as_float(b.w));
+            uint2 v;
+            v.x = *reinterpret_cast<const uint32_t*>(&lo);
+            v.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(hs + static_cast<size_t>(t) * (p.r + 8) + k) = v;
+        }
+        main_sync();
+    }
 
     // ---- phase U and store
     for (int blk = row0; blk < row1; blk += FA_ROWS) {
         float acc[2][NT][4];
         zero_acc<NT>(acc);
-        uh_block<NT>(p, acc, blk, row1, warp, gid, tig);
+        uh_block<NT, SIDE>(p, acc, blk, row1, hs, warp, gid, tig);
         const float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
         const int T = p.T, M = p.M;
         const __nv_bfloat16* yd = p.y_dense;
@@ -418,7 +496,7 @@ __global__ void __launch_bounds__(FA_THREADS) factored_kernel(const FactoredPara
     }
 
     // ---- the last CTA to finish re-arms the counters for the next call on this scratch buffer
-    __syncthreads();
+    main_sync();
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {

@@ -104,7 +104,8 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
  * when w_b != NULL (exactly one of the two must be given).
  *   x bf16 [T][N], y_dense bf16 [T][M], w_b bf16 [M][N], out bf16 [T][M].
  *   scratch: device buffer of at least ade_b200_factored_scratch_bytes(T, r) bytes.  It holds
- *   h = V^T x (bf16 [T][r]) and, at byte offset ade_b200_factored_sync_offset(T, r), three
+ *   h = V^T x (bf16 [T][r]; for T <= 16 two float32 partial sums [2][T][r], one per half of the
+ *   d_i axis) and, at byte offset ade_b200_factored_sync_offset(T, r), three
  *   32-bit words used to order the phases of the kernel: they must be ZERO before the first
  *   call that uses the buffer (one cudaMemset after allocation) and are left zero by every
  *   call that completes normally, so the buffer can be reused call after call.  Word 2 is a
@@ -112,7 +113,8 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
  *   zero the three words before reusing the buffer).  Calls that share a scratch buffer must
  *   not overlap on the GPU (use one buffer per stream).
  * Requirements: 1 <= T <= 128, M >= 1 (at most 320 rows per SM), N % 128 == 0, r % 128 == 0.
- * One kernel is launched on `stream` (one CTA per SM); the call does not synchronise.
+ * One kernel is launched on `stream` (one CTA per SM; for T <= 16 four extra warps per CTA compute
+ * h while the others already stream w_b); the call does not synchronise.
  */
 size_t ade_b200_factored_scratch_bytes(int T, int r);
 size_t ade_b200_factored_sync_offset(int T, int r);
@@ -129,8 +131,8 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
  * runs inside another framework's memory plan, under a fixed memory budget, or in a context where
  * cudaMalloc's implicit device synchronisation is not acceptable.  The entry point calls no cudaMalloc,
  * cudaFree or allocating library routine.
- *   Limit: 256 + 2 * T * r <= ADE_B200_STATIC_SCRATCH_BYTES (T * r <= 131072, e.g. T = 128 at r = 1024);
- *   larger products return ADE_ERR_SCRATCH.
+ *   Limit: ade_b200_factored_scratch_bytes(T, r) <= ADE_B200_STATIC_SCRATCH_BYTES, i.e. T * r <= 131072 for
+ *   T > 16 (e.g. T = 128 at r = 1024) and every supported rank for T <= 16; beyond it ADE_ERR_SCRATCH.
  *   The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
  *   current); make that first call outside any stream capture.
  *   All calls on a device share the one array, and it keeps the previous call's contents; every call
