@@ -24,6 +24,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxRowsCap = 320;    // rows of one CTA's slice that fit the shared-memory y buffer (T = 128)
+constexpr int kMaxSmem = 232448;     // opt-in dynamic shared memory per CTA on sm_100
 struct DeviceInfo {
     int ready = 0;      // 1 = usable, -1 = wrong architecture
     int sms = 0;
@@ -46,7 +47,7 @@ int device_info(const DeviceInfo** out) {
         if (major != 10) {
             d.ready = -1;
         } else {
-            const int smem = static_cast<int>(ade::recon_smem_bytes(ADE_B200_MAX_RANK / 128));
+            const int smem = kMaxSmem;
             if (!cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
                 return ADE_ERR_CUDA;
@@ -301,6 +302,7 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     p.N = d->N;
     p.r = d->r;
     const int ng = d->r / ADE_B200_GROUP;
+    if (ade::recon_smem_bytes(ng) > static_cast<size_t>(kMaxSmem)) return ADE_ERR_SHAPE;    // rank too large for one CTA's scale tables
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;
     if (dbg_acc)
