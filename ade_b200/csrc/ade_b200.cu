@@ -7,6 +7,7 @@
 
 #include "factored.cuh"
 #include "recon.cuh"
+#include "recon_strip.cuh"
 
 namespace {
 
@@ -49,7 +50,9 @@ int device_info(const DeviceInfo** out) {
         } else {
             const int smem = kMaxSmem;
             if (!cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
-                !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
                 return ADE_ERR_CUDA;
             if (!optin_factored<1>() || !optin_factored<2>() || !optin_factored<4>() || !optin_factored<8>() ||
                 !optin_factored<16>())
@@ -61,6 +64,38 @@ int device_info(const DeviceInfo** out) {
     if (d.ready < 0) return ADE_ERR_DEVICE;
     *out = &d;
     return ADE_OK;
+}
+
+// Tensor maps are encoded through the driver entry point, fetched once; the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+bool load_encode_tiled() {
+    if (g_encode_tiled) return true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (!cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q))) return false;
+    if (q != cudaDriverEntryPointSuccess || !fn) return false;
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    return true;
+}
+
+// Row-major (outer x inner) array of `esize`-byte elements, contiguous rows.
+bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esize, const void* base, uint64_t inner, uint64_t outer,
+                 uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * static_cast<uint64_t>(esize)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode_tiled(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = static_cast<int>(r);
+        return false;
+    }
+    return true;
 }
 
 int check_delta(const ade_delta_t* d) {
@@ -302,9 +337,26 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     p.N = d->N;
     p.r = d->r;
     const int ng = d->r / ADE_B200_GROUP;
-    if (ade::recon_smem_bytes(ng) > static_cast<size_t>(kMaxSmem)) return ADE_ERR_SHAPE;    // rank too large for one CTA's scale tables
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;
+    if (ng <= ade::RS_MAX_GROUPS) {
+        // ranks up to 512: the strip-resident kernel, all global traffic through tensor maps
+        if (!load_encode_tiled()) return ADE_ERR_CUDA;
+        ade::ReconMaps maps;
+        const uint64_t M = static_cast<uint64_t>(d->M), N = static_cast<uint64_t>(d->N), rb = static_cast<uint64_t>(d->r / 2);
+        if (!make_map_2d(&maps.wb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_b, N, M, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B) ||
+            !make_map_2d(&maps.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_out, N, M, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B) ||
+            !make_map_2d(&maps.uq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->uq, rb, M, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+            !make_map_2d(&maps.vq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->vq, rb, N, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return ADE_ERR_CUDA;
+        const size_t smem = ade::recon_strip_smem_bytes(ng);
+        if (dbg_acc)
+            ade::recon_strip_kernel<true><<<grid, ade::RS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p, maps);
+        else
+            ade::recon_strip_kernel<false><<<grid, ade::RS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p, maps);
+        return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    }
+    if (ade::recon_smem_bytes(ng) > static_cast<size_t>(kMaxSmem)) return ADE_ERR_SHAPE;    // rank too large for one CTA's scale tables
     if (dbg_acc)
         ade::recon_kernel<true><<<grid, ade::RC_THREADS, ade::recon_smem_bytes(ng), static_cast<cudaStream_t>(stream)>>>(p);
     else

@@ -1,0 +1,437 @@
+// Reconstructed application for ranks up to 512 (at most four groups of 128): same arithmetic, same
+// roundings and same tensor-core contraction as recon_kernel (recon.cuh), organised around a resident
+// strip of the U operand.
+//
+// Replaces ade_recon_int4_kernel (src/kernels.py:262-381); arithmetic order of src/quantization.py:303-315,
+// base add of src/serving.py:92.
+//
+// Every CTA owns a contiguous run of 128 x 128 output tiles in strip-major order (all n-tiles of a
+// 128-row strip, then the next strip), so the expanded int8 form of the strip's U rows (128 x r bytes)
+// is built once and stays in shared memory while only V tiles stream through.  All global traffic is
+// tensor-map (TMA) traffic issued by single threads; no CTA-wide barrier exists after set-up.
+//   warps 0-15  epilogue.  Warp w owns tensor-memory lanes 32*(w%4).. and 32 accumulator columns; it
+//               loads its own 32 x 32 box of W_b with one TMA copy at the start of a tile, merges in
+//               place and writes the box back with one TMA store.  Per group: tcgen05.ld, re-arm,
+//               release, FP32 rescale as in recon.cuh.
+//   warps 16-19 unpack: packed nibbles (raw ring filled by TMA) -> int8 minus zero-point, K-major
+//               128-byte-swizzled operand tiles; U items go to the resident strip, V items to a ring.
+//   warp  20    one thread issues tcgen05.mma.kind::i8 and the commits.
+//   warp  21    one thread issues the TMA copies of packed codes and V zero-points (raw ring).
+//   warp  22    scales: bf16 us / vs of the next tile -> float32 tables in shared memory (two buffers).
+// Every mbarrier wait is bounded as in recon.cuh (abort flag, status word, normal exit).
+#pragma once
+#include <cuda.h>
+
+#include "recon.cuh"
+
+namespace ade {
+
+constexpr int RS_MAX_GROUPS = 4;
+constexpr int RS_EPI_WARPS = 16;
+constexpr int RS_MMA_WARP = 20;
+constexpr int RS_LOAD_WARP = 21;
+constexpr int RS_SCALE_WARP = 22;
+constexpr int RS_THREADS = 23 * 32;
+constexpr int RS_B_STAGES = 3;                           // int8 V tiles in flight
+constexpr int RS_RAW_DEPTH = 4;                          // packed items in flight
+constexpr int RS_OPER_BYTES = RC_TILE * 128;             // one int8 operand tile of one group
+constexpr int RS_RAW_CODES = RC_TILE * 64;               // 128 rows x 64 bytes of nibbles
+constexpr int RS_RAW_SLOT = RS_RAW_CODES + 256;          // + 128 zero-points, padded
+constexpr int RS_ACC_STAGES = 2;
+constexpr int RS_TMEM_COLS = 256;
+constexpr int RS_BOX_BYTES = 32 * 64;                    // a warp's 32 x 32 bf16 box
+constexpr int RS_WB_BYTES = RS_EPI_WARPS * 2 * RS_BOX_BYTES;
+
+struct ReconMaps {
+    CUtensorMap wb;     // (M, N) bf16, box 32 x 32, 64-byte swizzle
+    CUtensorMap out;    // same geometry
+    CUtensorMap uq;     // (M, r/2) bytes, box 128 rows x 64 bytes
+    CUtensorMap vq;     // (N, r/2) bytes, box 128 rows x 64 bytes
+};
+
+// barrier indices (8 bytes each)
+constexpr int RS_BAR_RAW_FULL = 0;
+constexpr int RS_BAR_RAW_EMPTY = RS_BAR_RAW_FULL + RS_RAW_DEPTH;
+constexpr int RS_BAR_B_FULL = RS_BAR_RAW_EMPTY + RS_RAW_DEPTH;
+constexpr int RS_BAR_B_EMPTY = RS_BAR_B_FULL + RS_B_STAGES;
+constexpr int RS_BAR_A_FULL = RS_BAR_B_EMPTY + RS_B_STAGES;
+constexpr int RS_BAR_A_FREE = RS_BAR_A_FULL + RS_MAX_GROUPS;
+constexpr int RS_BAR_TFULL = RS_BAR_A_FREE + 1;
+constexpr int RS_BAR_TEMPTY = RS_BAR_TFULL + RS_ACC_STAGES;
+constexpr int RS_BAR_SC_FULL = RS_BAR_TEMPTY + RS_ACC_STAGES;
+constexpr int RS_BAR_SC_EMPTY = RS_BAR_SC_FULL + 2;
+constexpr int RS_BAR_WB = RS_BAR_SC_EMPTY + 2;
+constexpr int RS_BAR_COUNT = RS_BAR_WB + 2 * RS_EPI_WARPS;
+
+__host__ __device__ inline size_t recon_strip_smem_bytes(int ng) {
+    return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(RS_B_STAGES) * RS_OPER_BYTES +
+           RS_WB_BYTES + static_cast<size_t>(RS_RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * 2048 + RS_BAR_COUNT * 8 + 16;
+}
+
+// As unpack_store (recon.cuh), with the tile given by its shared-window address.
+__device__ __forceinline__ void unpack_store_s(uint32_t tile, int row, int c, uint4 q, uint32_t z) {
+    const uint32_t zk = 0x80808080u - z * 0x01010101u;
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = w[i] & 0x0F0F0F0Fu;
+        const uint32_t hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+        o[2 * i] = (lo + zk) ^ 0x80808080u;
+        o[2 * i + 1] = (hi + zk) ^ 0x80808080u;
+    }
+    const uint32_t rp = tile + row * 128;
+    const int sw = row & 7;
+    sts16(rp + (((2 * c) ^ sw) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+    sts16(rp + (((2 * c + 1) ^ sw) << 4), make_uint4(o[4], o[5], o[6], o[7]));
+}
+
+template <bool DBG>
+__global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconParams p, const __grid_constant__ ReconMaps maps) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw0 = smem_u32(smem_raw);
+    const uint32_t base = (raw0 + 1023u) & ~1023u;
+    const int ng = p.r >> 7;
+    const uint32_t a_res = base;                                          // [ng][128][128] int8, resident strip of U
+    const uint32_t b_st = a_res + ng * RS_OPER_BYTES;                     // [RS_B_STAGES][128][128] int8
+    const uint32_t wbuf = b_st + RS_B_STAGES * RS_OPER_BYTES;             // [16 warps][2][32][64 B]
+    const uint32_t rawr = wbuf + RS_WB_BYTES;                             // [RS_RAW_DEPTH][RS_RAW_SLOT]
+    const uint32_t scf = rawr + RS_RAW_DEPTH * RS_RAW_SLOT;               // [2][u | v][ng][128] float32
+    const uint32_t bars = scf + ng * 2048;
+    uint8_t* gen = smem_raw + (bars - raw0);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + RS_BAR_COUNT * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < RS_RAW_DEPTH; ++i) {
+            mbar_init(bar(RS_BAR_RAW_FULL + i), 1);
+            mbar_init(bar(RS_BAR_RAW_EMPTY + i), 4);
+        }
+        for (int i = 0; i < RS_B_STAGES; ++i) {
+            mbar_init(bar(RS_BAR_B_FULL + i), 4);
+            mbar_init(bar(RS_BAR_B_EMPTY + i), 1);
+        }
+        for (int i = 0; i < RS_MAX_GROUPS; ++i) mbar_init(bar(RS_BAR_A_FULL + i), 4);
+        mbar_init(bar(RS_BAR_A_FREE), 1);
+        for (int i = 0; i < RS_ACC_STAGES; ++i) {
+            mbar_init(bar(RS_BAR_TFULL + i), 1);
+            mbar_init(bar(RS_BAR_TEMPTY + i), RS_EPI_WARPS);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(RS_BAR_SC_FULL + i), 1);
+            mbar_init(bar(RS_BAR_SC_EMPTY + i), RS_EPI_WARPS);
+        }
+        for (int i = 0; i < 2 * RS_EPI_WARPS; ++i) mbar_init(bar(RS_BAR_WB + i), 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == RS_MMA_WARP) {
+        tmem_alloc(smem_u32(tmem_slot), RS_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_n = p.N >> 7;
+    const int ntiles = ((p.M + RC_TILE - 1) >> 7) * tiles_n;
+    const int t_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
+    const int t_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
+
+    if (warp < RS_EPI_WARPS) {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3, hh = warp >> 2;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * 32;
+        const uint32_t box0 = wbuf + warp * (2 * RS_BOX_BYTES);
+        const uint32_t own = lane * 64;                   // this thread's row of the box
+        const int swz = (lane >> 1) & 3;                  // 64-byte swizzle: 16-byte chunk index ^ bits 7-8 of the address
+        uint32_t magic4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(magic4[i]) : "n"(RC_MAGIC));
+#pragma unroll
+        for (int st = 0; st < RS_ACC_STAGES; ++st)
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) tmem_st16_fill(lane_addr + st * RC_TILE + ch * 16, magic4);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int st = 0; st < RS_ACC_STAGES; ++st) mbar_arrive(bar(RS_BAR_TEMPTY + st));
+            prefetch_tensormap(&maps.wb);
+            prefetch_tensormap(&maps.out);
+        }
+
+        uint32_t it = 0;
+        int j = 0;
+        for (int tile = t_begin; tile < t_end; ++tile, ++j) {
+            const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
+            const int m = m0 + row;
+            const bool live = m < p.M;
+            const uint32_t b = j & 1, jph = (j >> 1) & 1;
+            const uint32_t box = box0 + b * RS_BOX_BYTES;
+            if (lane == 0) {
+                bulk_wait_group_read<1>();               // the store that last read this box buffer is done with it
+                mbar_arrive_expect_tx(bar(RS_BAR_WB + 2 * warp + b), RS_BOX_BYTES);
+                tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, bar(RS_BAR_WB + 2 * warp + b));
+            }
+            wait_bounded(bar(RS_BAR_SC_FULL + b), jph, abort_flag, p.status, 5);
+            const uint32_t su = scf + b * (ng * 1024);
+            const uint32_t sv = su + ng * 512 + hh * 128;
+
+            uint64_t acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = 0ull;
+            const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
+
+            for (int g = 0; g < ng; ++g, ++it) {
+                const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
+                wait_bounded(bar(RS_BAR_TFULL + a), aph, abort_flag, p.status, 3);
+                tc_fence_after();
+                const float u = __uint_as_float(lds4(su + (g * RC_TILE + row) * 4));
+                const uint64_t uu = f2_pack(u, u);
+                const uint32_t tbase = lane_addr + a * RC_TILE;
+                const uint32_t svg = sv + g * 512;
+                uint32_t v[2][16];
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) tmem_ld16(tbase + ch * 16, v[ch]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(RS_BAR_TEMPTY + a));
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    const uint32_t (&vc)[16] = v[ch];
+                    uint4 fs[4];                         // column scales of 16 columns, all four loads in flight together
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) fs[i4] = lds16(svg + (ch * 4 + i4) * 16);
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        const uint4 f = fs[i4];
+                        const uint64_t fx = (static_cast<uint64_t>(f.y) << 32) | f.x, fy = (static_cast<uint64_t>(f.w) << 32) | f.z;
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {
+                            const int i = i4 * 4 + jj * 2;
+                            const uint64_t pf = f2_add(f2_pack(__uint_as_float(vc[i]), __uint_as_float(vc[i + 1])), neg_magic);
+                            const uint64_t s2 = f2_mul(uu, jj == 0 ? fx : fy);       // us * vs, exact
+                            acc[ch * 8 + i4 * 2 + jj] = f2_add(acc[ch * 8 + i4 * 2 + jj], f2_mul_rounded(pf, s2));
+                        }
+                    }
+                    if (DBG && live) {
+                        int32_t* d = p.dbg + (static_cast<size_t>(g) * p.M + m) * p.N + n0 + hh * 32 + ch * 16;
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4)
+                            *reinterpret_cast<int4*>(d + i) = make_int4(vc[i] - RC_MAGIC, vc[i + 1] - RC_MAGIC, vc[i + 2] - RC_MAGIC,
+                                                                        vc[i + 3] - RC_MAGIC);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(RS_BAR_SC_EMPTY + b));             // this warp is done with the scale tables
+            wait_bounded(bar(RS_BAR_WB + 2 * warp + b), jph, abort_flag, p.status, 6);
+            uint4 wv4[4];                                // 8 columns per 16-byte chunk
+#pragma unroll
+            for (int c = 0; c < 4; ++c) wv4[c] = lds16(box + own + ((c ^ swz) << 4));
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t wq[4] = {wv4[c].x, wv4[c].y, wv4[c].z, wv4[c].w};
+                uint32_t oq[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint64_t b2 = f2_pack(__uint_as_float(wq[e] << 16), __uint_as_float(wq[e] & 0xFFFF0000u));
+                    float o0, o1;
+                    f2_unpack(f2_add(b2, acc[c * 4 + e]), o0, o1);
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(o0, o1);
+                    oq[e] = *reinterpret_cast<const uint32_t*>(&o);
+                }
+                sts16(box + own + ((c ^ swz) << 4), make_uint4(oq[0], oq[1], oq[2], oq[3]));
+            }
+            fence_proxy_async_smem();                    // merged box visible to the TMA store
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&maps.out, n0 + hh * 32, m0 + q * 32, box);
+                bulk_commit_group();
+            }
+        }
+        if (lane == 0) bulk_wait_group<0>();
+    } else if (warp < RS_MMA_WARP) {
+        // ------------------------------------------------------------------ unpack
+        const int pt = threadIdx.x - RS_EPI_WARPS * 32;
+        const int c = pt & 3, rbase = pt >> 2;
+        uint32_t ri = 0, bi = 0, sk = 0;
+        int cur_strip = -1;
+        uint32_t za_pack[4] = {0, 0, 0, 0};               // zero-points of this thread's four U rows, one byte per group
+        for (int tile = t_begin; tile < t_end; ++tile) {
+            const int strip = tile / tiles_n;
+            if (strip != cur_strip) {
+                cur_strip = strip;
+                const int m0 = strip << 7;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int m = m0 + rbase + 32 * i;
+                    uint32_t z = 0;
+                    if (m < p.M)
+                        for (int g = 0; g < ng; ++g) z |= static_cast<uint32_t>(p.uz[static_cast<size_t>(m) * ng + g]) << (8 * g);
+                    za_pack[i] = z;
+                }
+                if (sk > 0) wait_bounded(bar(RS_BAR_A_FREE), (sk - 1) & 1, abort_flag, p.status, 7);   // old strip's MMAs retired
+                for (int g = 0; g < ng; ++g, ++ri) {
+                    const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
+                    wait_bounded(bar(RS_BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                    const uint32_t rs = rawr + slot * RS_RAW_SLOT;
+                    uint4 qa[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) qa[i] = lds16(rs + (rbase + 32 * i) * 64 + c * 16);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(RS_BAR_RAW_EMPTY + slot));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        unpack_store_s(a_res + g * RS_OPER_BYTES, rbase + 32 * i, c, qa[i], (za_pack[i] >> (8 * g)) & 0xFFu);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(RS_BAR_A_FULL + g));
+                }
+                ++sk;
+            }
+            for (int g = 0; g < ng; ++g, ++ri, ++bi) {
+                const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
+                wait_bounded(bar(RS_BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                const uint32_t rs = rawr + slot * RS_RAW_SLOT;
+                uint4 qb[4];
+                uint32_t zb[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    qb[i] = lds16(rs + (rbase + 32 * i) * 64 + c * 16);
+                    zb[i] = lds1(rs + RS_RAW_CODES + rbase + 32 * i);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(RS_BAR_RAW_EMPTY + slot));
+                const uint32_t s = bi % RS_B_STAGES, bph = (bi / RS_B_STAGES) & 1;
+                wait_bounded(bar(RS_BAR_B_EMPTY + s), bph ^ 1, abort_flag, p.status, 2);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) unpack_store_s(b_st + s * RS_OPER_BYTES, rbase + 32 * i, c, qb[i], zb[i]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(RS_BAR_B_FULL + s));
+            }
+        }
+    } else if (warp == RS_MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, bi = 0, k = 0;
+            for (int tile = t_begin; tile < t_end; ++tile) {
+                const bool first = tile == t_begin || tile % tiles_n == 0;
+                const bool last = tile == t_end - 1 || (tile + 1) % tiles_n == 0;
+                for (int g = 0; g < ng; ++g, ++it, ++bi) {
+                    const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
+                    const uint32_t s = bi % RS_B_STAGES, bph = (bi / RS_B_STAGES) & 1;
+                    wait_bounded(bar(RS_BAR_TEMPTY + a), aph, abort_flag, p.status, 4);
+                    wait_bounded(bar(RS_BAR_B_FULL + s), bph, abort_flag, p.status, 1);
+                    if (first) wait_bounded(bar(RS_BAR_A_FULL + g), k & 1, abort_flag, p.status, 9);
+                    tc_fence_after();
+                    const uint64_t ad = smem_desc_k_sw128(a_res + g * RS_OPER_BYTES);
+                    const uint64_t bd = smem_desc_k_sw128(b_st + s * RS_OPER_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * kk, bd + 2 * kk, RC_IDESC, 1u);
+                    tc_commit(bar(RS_BAR_B_EMPTY + s));
+                    tc_commit(bar(RS_BAR_TFULL + a));
+                    if (last && g == ng - 1) tc_commit(bar(RS_BAR_A_FREE));    // the strip of U may be overwritten
+                }
+                if (last) ++k;
+            }
+        }
+        __syncwarp();
+    } else if (warp == RS_LOAD_WARP) {
+        // ------------------------------------------------------------------ packed codes -> raw ring
+        if (lane == 0) {
+            prefetch_tensormap(&maps.uq);
+            prefetch_tensormap(&maps.vq);
+            uint32_t ri = 0;
+            int cur_strip = -1;
+            for (int tile = t_begin; tile < t_end; ++tile) {
+                const int strip = tile / tiles_n, n0 = (tile % tiles_n) << 7;
+                if (strip != cur_strip) {
+                    cur_strip = strip;
+                    for (int g = 0; g < ng; ++g, ++ri) {
+                        const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
+                        wait_bounded(bar(RS_BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                        mbar_arrive_expect_tx(bar(RS_BAR_RAW_FULL + slot), RS_RAW_CODES);
+                        tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.uq, g * 64, strip << 7, bar(RS_BAR_RAW_FULL + slot));
+                    }
+                }
+                for (int g = 0; g < ng; ++g, ++ri) {
+                    const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
+                    wait_bounded(bar(RS_BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                    mbar_arrive_expect_tx(bar(RS_BAR_RAW_FULL + slot), RS_RAW_CODES + 128);
+                    tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.vq, g * 64, n0, bar(RS_BAR_RAW_FULL + slot));
+                    bulk_g2s(rawr + slot * RS_RAW_SLOT + RS_RAW_CODES, p.vz + static_cast<size_t>(g) * p.N + n0, 128,
+                             bar(RS_BAR_RAW_FULL + slot));
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ scale tables, one tile ahead
+        int j = 0;
+        for (int tile = t_begin; tile < t_end; ++tile, ++j) {
+            const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
+            const uint32_t b = j & 1, jph = (j >> 1) & 1;
+            const uint32_t su = scf + b * (ng * 1024), sv = su + ng * 512;
+            // us: rows m0.. of a (M, ng) array = 128 * ng consecutive bf16; vs: 128 consecutive bf16 per group
+            uint4 vu[2], vv[2];
+            const long long u_first = static_cast<long long>(m0) * ng, u_total = static_cast<long long>(p.M) * ng;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int vi = lane + 32 * t;             // 16-byte vector index, 16 * ng of each kind
+                vu[t] = make_uint4(0, 0, 0, 0);
+                vv[t] = make_uint4(0, 0, 0, 0);
+                if (vi < 16 * ng) {
+                    const long long e0 = u_first + 8 * vi;
+                    if (e0 + 8 <= u_total) {
+                        vu[t] = ldg16(p.us + e0);
+                    } else {
+                        uint32_t w[4] = {0, 0, 0, 0};
+                        for (int e = 0; e < 8; ++e)
+                            if (e0 + e < u_total) w[e >> 1] |= static_cast<uint32_t>(p.us[e0 + e]) << (16 * (e & 1));
+                        vu[t] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    vv[t] = ldg16(p.vs + static_cast<size_t>(vi >> 4) * p.N + n0 + (vi & 15) * 8);
+                }
+            }
+            wait_bounded(bar(RS_BAR_SC_EMPTY + b), jph ^ 1, abort_flag, p.status, 11);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int vi = lane + 32 * t;
+                if (vi < 16 * ng) {
+                    const uint32_t wu[4] = {vu[t].x, vu[t].y, vu[t].z, vu[t].w};
+                    const uint32_t wv[4] = {vv[t].x, vv[t].y, vv[t].z, vv[t].w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int eu = 8 * vi + e;        // element of the strip: row * ng + group
+                        const int r_ = eu / ng, g_ = eu - r_ * ng;
+                        const uint32_t hu = (e & 1) ? (wu[e >> 1] & 0xFFFF0000u) : (wu[e >> 1] << 16);
+                        sts4(su + (g_ * RC_TILE + r_) * 4, hu);
+                        const uint32_t hv = (e & 1) ? (wv[e >> 1] & 0xFFFF0000u) : (wv[e >> 1] << 16);
+                        sts4(sv + ((vi >> 4) * RC_TILE + (vi & 15) * 8 + e) * 4, hv);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(RS_BAR_SC_FULL + b));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == RS_MMA_WARP) tmem_dealloc(tmem_base, RS_TMEM_COLS);
+}
+
+}  // namespace ade
