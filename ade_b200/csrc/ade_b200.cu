@@ -336,6 +336,7 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     p.M = d->M;
     p.N = d->N;
     p.r = d->r;
+    p.one = 1.0f;
     const int ng = d->r / ADE_B200_GROUP;
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;

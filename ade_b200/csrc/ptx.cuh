@@ -243,6 +243,11 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     return d;
 }
 
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
 // a * b per lane with two scalar mul.rn.f32: the assembler contracts a packed mul.rn.f32x2 with a
 // following add.rn.f32x2 into one fused multiply-add (one rounding instead of two); scalar
 // mul.rn is never contracted, so this keeps the product's own rounding

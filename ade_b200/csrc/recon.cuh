@@ -62,6 +62,7 @@ struct ReconParams {
     int32_t* dbg;
     int* status;
     int M, N, r;
+    float one;      // 1.0f, set by the host: a value the assembler cannot fold (see recon_strip.cuh)
 };
 
 constexpr int RC_WB_ROW = 272;                          // one tile row: 256 bytes of bf16, padded (bank spread)

@@ -37,10 +37,12 @@ constexpr int RS_RAW_DEPTH = 4;                          // packed items in flig
 constexpr int RS_OPER_BYTES = RC_TILE * 128;             // one int8 operand tile of one group
 constexpr int RS_RAW_CODES = RC_TILE * 64;               // 128 rows x 64 bytes of nibbles
 constexpr int RS_RAW_SLOT = RS_RAW_CODES + 256;          // + 128 zero-points, padded
-constexpr int RS_ACC_STAGES = 2;
-constexpr int RS_TMEM_COLS = 256;
+constexpr int RS_ACC_STAGES = 4;                        // 128-column accumulators in tensor memory (all 512 columns)
+constexpr int RS_TMEM_COLS = RS_ACC_STAGES * RC_TILE;
 constexpr int RS_BOX_BYTES = 32 * 64;                    // a warp's 32 x 32 bf16 box
 constexpr int RS_WB_BYTES = RS_EPI_WARPS * 2 * RS_BOX_BYTES;
+// scale tables of one tile, per group: us as float32 [128], then per column pair {vs, vs, -m vs, -m vs} (m = 1.5 * 2^23)
+constexpr int RS_SC_BYTES = 512 + 1024;
 
 struct ReconMaps {
     CUtensorMap wb;     // (M, N) bf16, box 32 x 32, 64-byte swizzle
@@ -65,7 +67,7 @@ constexpr int RS_BAR_COUNT = RS_BAR_WB + 2 * RS_EPI_WARPS;
 
 __host__ __device__ inline size_t recon_strip_smem_bytes(int ng) {
     return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(RS_B_STAGES) * RS_OPER_BYTES +
-           RS_WB_BYTES + static_cast<size_t>(RS_RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * 2048 + RS_BAR_COUNT * 8 + 16;
+           RS_WB_BYTES + static_cast<size_t>(RS_RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + RS_BAR_COUNT * 8 + 16;
 }
 
 // As unpack_store (recon.cuh), with the tile given by its shared-window address.
@@ -96,8 +98,8 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
     const uint32_t b_st = a_res + ng * RS_OPER_BYTES;                     // [RS_B_STAGES][128][128] int8
     const uint32_t wbuf = b_st + RS_B_STAGES * RS_OPER_BYTES;             // [16 warps][2][32][64 B]
     const uint32_t rawr = wbuf + RS_WB_BYTES;                             // [RS_RAW_DEPTH][RS_RAW_SLOT]
-    const uint32_t scf = rawr + RS_RAW_DEPTH * RS_RAW_SLOT;               // [2][u | v][ng][128] float32
-    const uint32_t bars = scf + ng * 2048;
+    const uint32_t scf = rawr + RS_RAW_DEPTH * RS_RAW_SLOT;               // [2][ng][RS_SC_BYTES] scale tables
+    const uint32_t bars = scf + ng * RS_SC_BYTES * 2;
     uint8_t* gen = smem_raw + (bars - raw0);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + RS_BAR_COUNT * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -180,48 +182,46 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, bar(RS_BAR_WB + 2 * warp + b));
             }
             wait_bounded(bar(RS_BAR_SC_FULL + b), jph, abort_flag, p.status, 5);
-            const uint32_t su = scf + b * (ng * 1024);
-            const uint32_t sv = su + ng * 512 + hh * 128;
+            const uint32_t sct = scf + b * (ng * RS_SC_BYTES);          // this tile's tables
 
             uint64_t acc[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] = 0ull;
-            const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
+            const uint64_t one2 = f2_pack(p.one, p.one);  // 1.0f from the kernel parameters: acc + t as fma(t, 1, acc), never contracted
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                 wait_bounded(bar(RS_BAR_TFULL + a), aph, abort_flag, p.status, 3);
                 tc_fence_after();
-                const float u = __uint_as_float(lds4(su + (g * RC_TILE + row) * 4));
+                const uint32_t scg = sct + g * RS_SC_BYTES;
+                const float u = __uint_as_float(lds4(scg + row * 4));
                 const uint64_t uu = f2_pack(u, u);
                 const uint32_t tbase = lane_addr + a * RC_TILE;
-                const uint32_t svg = sv + g * 512;
+                const uint32_t svg = scg + 512 + hh * 256;               // 16 column pairs of this warp
                 uint32_t v[2][16];
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) tmem_ld16(tbase + ch * 16, v[ch]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(RS_BAR_TEMPTY + a));
+                for (int ch = 0; ch < 2; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);      // re-arm, completes under the arithmetic
+                // The accumulator started at RC_MAGIC, so its bits are the float m + P (m = 1.5 * 2^23), exactly.
+                // x = fma(m + P, vs, -m vs) = P vs exactly (|P| < 2^15, vs has 8 significant bits);
+                // t = x * us is P * (us * vs) rounded once, as the reference rounds it; acc + t rounded once.
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     const uint32_t (&vc)[16] = v[ch];
-                    uint4 fs[4];                         // column scales of 16 columns, all four loads in flight together
 #pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) fs[i4] = lds16(svg + (ch * 4 + i4) * 16);
+                    for (int h4 = 0; h4 < 2; ++h4) {
+                        uint4 fs[4];
 #pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) {
-                        const uint4 f = fs[i4];
-                        const uint64_t fx = (static_cast<uint64_t>(f.y) << 32) | f.x, fy = (static_cast<uint64_t>(f.w) << 32) | f.z;
+                        for (int i4 = 0; i4 < 4; ++i4) fs[i4] = lds16(svg + (ch * 8 + h4 * 4 + i4) * 16);
 #pragma unroll
-                        for (int jj = 0; jj < 2; ++jj) {
-                            const int i = i4 * 4 + jj * 2;
-                            const uint64_t pf = f2_add(f2_pack(__uint_as_float(vc[i]), __uint_as_float(vc[i + 1])), neg_magic);
-                            const uint64_t s2 = f2_mul(uu, jj == 0 ? fx : fy);       // us * vs, exact
-                            acc[ch * 8 + i4 * 2 + jj] = f2_add(acc[ch * 8 + i4 * 2 + jj], f2_mul_rounded(pf, s2));
+                        for (int i4 = 0; i4 < 4; ++i4) {
+                            const int k = h4 * 4 + i4;       // column pair inside this chunk of 16 columns
+                            const uint64_t vs2 = (static_cast<uint64_t>(fs[i4].y) << 32) | fs[i4].x;
+                            const uint64_t c2 = (static_cast<uint64_t>(fs[i4].w) << 32) | fs[i4].z;
+                            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(vc[2 * k]), __uint_as_float(vc[2 * k + 1])), vs2, c2);
+                            acc[ch * 8 + k] = f2_fma(f2_mul(x2, uu), one2, acc[ch * 8 + k]);
                         }
                     }
                     if (DBG && live) {
@@ -232,6 +232,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                                                                         vc[i + 3] - RC_MAGIC);
                     }
                 }
+                tmem_st_wait();                          // accumulator stage re-armed: hand it back
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(RS_BAR_TEMPTY + a));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(RS_BAR_SC_EMPTY + b));             // this warp is done with the scale tables
@@ -384,7 +388,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         for (int tile = t_begin; tile < t_end; ++tile, ++j) {
             const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
             const uint32_t b = j & 1, jph = (j >> 1) & 1;
-            const uint32_t su = scf + b * (ng * 1024), sv = su + ng * 512;
+            const uint32_t sct = scf + b * (ng * RS_SC_BYTES);
             // us: rows m0.. of a (M, ng) array = 128 * ng consecutive bf16; vs: 128 consecutive bf16 per group
             uint4 vu[2], vv[2];
             const long long u_first = static_cast<long long>(m0) * ng, u_total = static_cast<long long>(p.M) * ng;
@@ -418,9 +422,14 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                         const int eu = 8 * vi + e;        // element of the strip: row * ng + group
                         const int r_ = eu / ng, g_ = eu - r_ * ng;
                         const uint32_t hu = (e & 1) ? (wu[e >> 1] & 0xFFFF0000u) : (wu[e >> 1] << 16);
-                        sts4(su + (g_ * RC_TILE + r_) * 4, hu);
-                        const uint32_t hv = (e & 1) ? (wv[e >> 1] & 0xFFFF0000u) : (wv[e >> 1] << 16);
-                        sts4(sv + ((vi >> 4) * RC_TILE + (vi & 15) * 8 + e) * 4, hv);
+                        sts4(sct + g_ * RS_SC_BYTES + r_ * 4, hu);
+                    }
+                    const uint32_t dst = sct + (vi >> 4) * RS_SC_BYTES + 512 + (vi & 15) * 64;   // 4 column pairs of group vi / 16
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float v0 = __uint_as_float(wv[e] << 16), v1 = __uint_as_float(wv[e] & 0xFFFF0000u);
+                        sts16(dst + e * 16, make_uint4(__float_as_uint(v0), __float_as_uint(v1), __float_as_uint(__fmul_rn(v0, -12582912.0f)),
+                                                       __float_as_uint(__fmul_rn(v1, -12582912.0f))));
                     }
                 }
             }
