@@ -68,6 +68,10 @@ __device__ __forceinline__ uint4 lds16(uint32_t a) {
 __device__ __forceinline__ void sts16(uint32_t a, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// two packed float pairs (four consecutive floats) straight into 64-bit registers
+__device__ __forceinline__ void lds_f2x2(uint32_t a, uint64_t& p0, uint64_t& p1) {
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(p0), "=l"(p1) : "r"(a) : "memory");
+}
 __device__ __forceinline__ uint32_t lds4(uint32_t a) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");

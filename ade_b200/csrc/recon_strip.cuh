@@ -41,8 +41,8 @@ constexpr int RS_ACC_STAGES = 4;                        // 128-column accumulato
 constexpr int RS_TMEM_COLS = RS_ACC_STAGES * RC_TILE;
 constexpr int RS_BOX_BYTES = 32 * 64;                    // a warp's 32 x 32 bf16 box
 constexpr int RS_WB_BYTES = RS_EPI_WARPS * 2 * RS_BOX_BYTES;
-// scale tables of one tile, per group: us as float32 [128], then per column pair {vs, vs, -m vs, -m vs} (m = 1.5 * 2^23)
-constexpr int RS_SC_BYTES = 512 + 1024;
+// scale tables of one tile, per group: us of the 128 rows, then vs of the 128 columns, as float32
+constexpr int RS_SC_BYTES = 512 + 512;
 
 struct ReconMaps {
     CUtensorMap wb;     // (M, N) bf16, box 32 x 32, 64-byte swizzle
@@ -196,32 +196,29 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 const uint32_t scg = sct + g * RS_SC_BYTES;
                 const float u = __uint_as_float(lds4(scg + row * 4));
                 const uint64_t uu = f2_pack(u, u);
+                const float um = __fmul_rn(u, -12582912.0f);            // -m us, exact (m = 1.5 * 2^23)
+                const uint64_t cc = f2_pack(um, um);
                 const uint32_t tbase = lane_addr + a * RC_TILE;
-                const uint32_t svg = scg + 512 + hh * 256;               // 16 column pairs of this warp
-                uint32_t v[2][16];
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) tmem_ld16(tbase + ch * 16, v[ch]);
-                tmem_ld_wait();
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);      // re-arm, completes under the arithmetic
-                // The accumulator started at RC_MAGIC, so its bits are the float m + P (m = 1.5 * 2^23), exactly.
-                // x = fma(m + P, vs, -m vs) = P vs exactly (|P| < 2^15, vs has 8 significant bits);
-                // t = x * us is P * (us * vs) rounded once, as the reference rounds it; acc + t rounded once.
+                const uint32_t svg = scg + 512 + hh * 128;               // vs of this warp's 32 columns
+                // The accumulator started at RC_MAGIC, so its bits are the float m + P, exactly.
+                // x = fma(m + P, us, -m us) = P us exactly (|P| < 2^15, us has 8 significant bits);
+                // t = x * vs is P * (us * vs) rounded once, as the reference rounds it; acc + t rounded once.
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    const uint32_t (&vc)[16] = v[ch];
+                    uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
+                    tmem_ld16(tbase + ch * 16, vc);
+                    tmem_ld_wait();
+                    tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
 #pragma unroll
                     for (int h4 = 0; h4 < 2; ++h4) {
-                        uint4 fs[4];
+                        uint64_t vs2[4];                 // vs of 8 columns as packed pairs, both loads in flight together
+                        lds_f2x2(svg + (ch * 4 + h4 * 2) * 16, vs2[0], vs2[1]);
+                        lds_f2x2(svg + (ch * 4 + h4 * 2 + 1) * 16, vs2[2], vs2[3]);
 #pragma unroll
-                        for (int i4 = 0; i4 < 4; ++i4) fs[i4] = lds16(svg + (ch * 8 + h4 * 4 + i4) * 16);
-#pragma unroll
-                        for (int i4 = 0; i4 < 4; ++i4) {
-                            const int k = h4 * 4 + i4;       // column pair inside this chunk of 16 columns
-                            const uint64_t vs2 = (static_cast<uint64_t>(fs[i4].y) << 32) | fs[i4].x;
-                            const uint64_t c2 = (static_cast<uint64_t>(fs[i4].w) << 32) | fs[i4].z;
-                            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(vc[2 * k]), __uint_as_float(vc[2 * k + 1])), vs2, c2);
-                            acc[ch * 8 + k] = f2_fma(f2_mul(x2, uu), one2, acc[ch * 8 + k]);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int k = h4 * 4 + kk;
+                            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(vc[2 * k]), __uint_as_float(vc[2 * k + 1])), uu, cc);
+                            acc[ch * 8 + k] = f2_fma(f2_mul(x2, vs2[kk]), one2, acc[ch * 8 + k]);
                         }
                     }
                     if (DBG && live) {
@@ -424,13 +421,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                         const uint32_t hu = (e & 1) ? (wu[e >> 1] & 0xFFFF0000u) : (wu[e >> 1] << 16);
                         sts4(sct + g_ * RS_SC_BYTES + r_ * 4, hu);
                     }
-                    const uint32_t dst = sct + (vi >> 4) * RS_SC_BYTES + 512 + (vi & 15) * 64;   // 4 column pairs of group vi / 16
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float v0 = __uint_as_float(wv[e] << 16), v1 = __uint_as_float(wv[e] & 0xFFFF0000u);
-                        sts16(dst + e * 16, make_uint4(__float_as_uint(v0), __float_as_uint(v1), __float_as_uint(__fmul_rn(v0, -12582912.0f)),
-                                                       __float_as_uint(__fmul_rn(v1, -12582912.0f))));
-                    }
+                    const uint32_t dst = sct + (vi >> 4) * RS_SC_BYTES + 512 + (vi & 15) * 32;   // 8 columns of group vi / 16
+                    sts16(dst, make_uint4(wv[0] << 16, wv[0] & 0xFFFF0000u, wv[1] << 16, wv[1] & 0xFFFF0000u));
+                    sts16(dst + 16, make_uint4(wv[2] << 16, wv[2] & 0xFFFF0000u, wv[3] << 16, wv[3] & 0xFFFF0000u));
                 }
             }
             __syncwarp();
