@@ -55,8 +55,8 @@ def factored_bytes(M, N, r, T, fused):
 
 WORK_OPS = sum(delta_ops(M, N, RANK) for _, M, N in MODULES)
 # dram__bytes_read.sum + dram__bytes_write.sum of one reconstruction launch on gate_proj, from the ncu capture
-# summarised in profiles/recon_kernel_gate_proj_r512.md (94.3 MB + 50.3 MB; part of W' is still in L2 at exit)
-RECON_TRAFFIC_BYTES = 144.6e6
+# summarised in profiles/recon_kernel_gate_proj_r512.md (95.5 MB + 51.6 MB; part of W' is still in L2 at exit)
+RECON_TRAFFIC_BYTES = 147.1e6
 
 
 def measured_peaks():
@@ -344,7 +344,7 @@ def run_ade(args):
                     "d2h_bytes_per_step": sum(2 * TOKENS * M for _, M, _ in MODULES)},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": RECON_TRAFFIC_BYTES, "peak_kind": peak_kind, "kernel": "recon_kernel", "us_per_launch": recon_ms * 1e3,
+                         "traffic": RECON_TRAFFIC_BYTES, "peak_kind": peak_kind, "kernel": "recon_strip_kernel", "us_per_launch": recon_ms * 1e3,
                          "int8_tops_kernel_only": (WORK_OPS / 3) / (recon_ms * 1e-3) / 1e12},
             "cpu_baseline": {"value": cpu_tops, "unit": UNIT, "cores": cpu_threads, "kind": "port",
                              "sample": f"{cpu_rows} of 11008 rows of gate_proj: reconstruct + base add + x W'^T, {cpu_sec:.2f} s per pass"},

@@ -42,6 +42,13 @@ extern "C" {
 #define ADE_DEV_TIMEOUT_EMPTY 2     /* unpack warps gave up waiting for a free operand stage */
 #define ADE_DEV_TIMEOUT_TMEM_FULL 3 /* epilogue gave up waiting for an accumulator */
 #define ADE_DEV_TIMEOUT_TMEM_EMPTY 4/* MMA warp gave up waiting for a free accumulator */
+#define ADE_DEV_TIMEOUT_SCALES 5     /* epilogue gave up waiting for the scale tables of a tile */
+#define ADE_DEV_TIMEOUT_BASE 6       /* epilogue gave up waiting for its box of w_b */
+#define ADE_DEV_TIMEOUT_STRIP_FREE 7 /* unpack warps gave up waiting for the resident U strip to retire */
+#define ADE_DEV_TIMEOUT_RAW_FULL 8   /* unpack warps gave up waiting for packed codes */
+#define ADE_DEV_TIMEOUT_STRIP_FULL 9 /* MMA warp gave up waiting for the resident U strip */
+#define ADE_DEV_TIMEOUT_RAW_EMPTY 10 /* load thread gave up waiting for a free raw slot */
+#define ADE_DEV_TIMEOUT_SCALES_FREE 11 /* scale warp gave up waiting for a free table buffer */
 
 /*
  * Device stored form of one compressed module (all pointers are device memory, 16-byte
@@ -152,7 +159,9 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
  *
  * the arithmetic of src/quantization.py:303-315 followed by the add of src/serving.py:92,
  * in the same order and with the same float32 roundings.  P_g is contracted with
- * tcgen05 kind::i8 MMAs into tensor memory.
+ * tcgen05 kind::i8 MMAs into tensor memory.  Ranks up to 512 run a kernel that keeps a 128-row strip
+ * of U expanded in shared memory and moves all global data with TMA (tensor maps are encoded per call
+ * on the host; no device memory is allocated); larger ranks run the general kernel.
  *   w_b, w_out bf16 [M][N] (may not alias).  Requirements: N % 128 == 0, r % 128 == 0, M >= 1.
  *   dbg_acc: optional int32 [ng][M][N]; when non-NULL every P_g is also written there.
  *   status_dev: optional device int; set to a non-zero ADE_DEV_* code if a bounded wait
