@@ -25,6 +25,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxRowsCap = 320;    // rows of one CTA's slice that fit the shared-memory y buffer (T = 128)
+constexpr size_t kFifoMinStream = 400 * 1024;   // bytes of W_b per CTA from which the FIFO pays off
 constexpr int kMaxSmem = 232448;     // opt-in dynamic shared memory per CTA on sm_100
 struct DeviceInfo {
     int ready = 0;      // 1 = usable, -1 = wrong architecture
@@ -146,8 +147,24 @@ void set_row_split(ade::FactoredParams& p, int grid) {
 }
 
 template <int NT, bool FUSE>
-int launch_factored_one(const ade::FactoredParams& p, int grid, cudaStream_t st) {
-    const size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
+int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
+    size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
+    p.stages = 0;
+    // Decode sizes with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than registers allow).
+    // Short streams (a 4096 x 4096 module is 227 KB per CTA) are faster with the register prefetch: the deep
+    // FIFO raises the loaded memory latency, and the h hand-over pays it several times.
+    const size_t stream_bytes = static_cast<size_t>(p.M) * p.N * 2 / static_cast<size_t>(grid);
+    if (FUSE && ade::fa_side(NT) && stream_bytes >= kFifoMinStream) {
+        const size_t room = (static_cast<size_t>(kMaxSmem) - smem) / ade::fa_fifo_item(NT);
+        p.stages = room >= 2 ? static_cast<int>(room < static_cast<size_t>(ade::FA_FIFO_MAX) ? room : ade::FA_FIFO_MAX) : 0;
+        smem += static_cast<size_t>(p.stages) * ade::fa_fifo_item(NT);
+    }
+    if constexpr (FUSE && ade::fa_side(NT)) {
+        if (p.stages >= 2) {
+            ade::factored_kernel<NT, true, true><<<grid, ade::fa_threads(NT), smem, st>>>(p);
+            return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+        }
+    }
     ade::factored_kernel<NT, FUSE><<<grid, ade::fa_threads(NT), smem, st>>>(p);
     return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
@@ -159,7 +176,12 @@ int launch_factored(const ade::FactoredParams& p, int grid, cudaStream_t st) {
 
 template <int NT>
 bool optin_factored() {
-    const int smem = static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, NT <= 2 ? 16 : 0, ADE_B200_MAX_RANK));
+    const int smem = ade::fa_side(NT) ? kMaxSmem
+                                      : static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, 0, ADE_B200_MAX_RANK));
+    if constexpr (ade::fa_side(NT)) {
+        if (!cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)))
+            return false;
+    }
     return cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) &&
            cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, NT <= 2 ? 16 : 0, ADE_B200_MAX_RANK))));

@@ -61,12 +61,29 @@ struct FactoredParams {
     int T, M, N, r;
     int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
     int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
+    int stages;                    // depth of the shared-memory FIFO that streams W_b (0: register prefetch)
 };
 
+// Side warps stage the V codes, scales and zero-points of up to FA_STAGE_CHUNKS chunks of 128 columns per warp
+// (16 ranks x 64 bytes of codes, 256 bytes of scales, 128 bytes of zero-points per chunk) with cp.async, so that
+// a whole wave of chunks is one memory round trip.  The region is reused for h (bf16 [T][r + 8]) in phase U.
+constexpr int FA_STAGE_CHUNKS = 4;
+constexpr int FA_STAGE_CHUNK_BYTES = 16 * 64 + 256 + 128;
+__host__ __device__ constexpr size_t fa_side_region(int T, int r) {
+    const size_t hs = static_cast<size_t>(T) * (r + 8) * 2 + 16;
+    const size_t st = static_cast<size_t>(FA_SIDE_WARPS) * FA_STAGE_CHUNKS * FA_STAGE_CHUNK_BYTES;
+    return hs > st ? hs : st;
+}
+// one FIFO item = one 64-column block of 32 rows of W_b (8 x 16 bytes per main thread) and the matching
+// activations (2 x 16 bytes per 8 tokens)
+__host__ __device__ constexpr int fa_fifo_item(int NT) { return (8 + 2 * NT) * 16 * FA_THREADS; }
+constexpr int FA_FIFO_MAX = 5;
+
+// without the FIFO; the launch adds stages * fa_fifo_item(NT) in front
 __host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap, int T, int r) {
     return (static_cast<size_t>(FA_WARPS) * 32 * 33 + (fa_side(NT) ? FA_SIDE_WARPS * 32 * 17 : 0) +
             static_cast<size_t>(rows_cap) * (8 * NT + 1)) * sizeof(float) +
-           (fa_side(NT) ? static_cast<size_t>(T) * (r + 8) * 2 + 16 : 0);
+           (fa_side(NT) ? fa_side_region(T, r) : 0);
 }
 
 // one packed word (8 codes) -> 4 bf16x2 registers holding 128 + code, codes in natural order
@@ -75,6 +92,19 @@ __device__ __forceinline__ void unpack8_bf16(uint32_t w, uint32_t (&e)[4]) {
     e[1] = ((w >> 4) & 0x000F000Fu) | kBf2_128;
     e[2] = ((w >> 8) & 0x000F000Fu) | kBf2_128;
     e[3] = ((w >> 12) & 0x000F000Fu) | kBf2_128;
+}
+
+__device__ __forceinline__ void fa_cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void fa_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void fa_cp_async_wait(int n) {      // at most n of this thread's groups still in flight
+    switch (n) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    }
 }
 
 // Sum the 8 warps' partial tiles in a fixed order.  acc[mt][nt][4] covers 32 rows x 8*NT tokens;
@@ -158,9 +188,9 @@ __device__ __forceinline__ void xv_load(XvRegs<NT>& R, const FactoredParams& p, 
 
 // TEAM warps (the CTA's 8 main warps, or its 4 side warps) split the d_i axis in chunks of 128 columns.
 // Chunks [c_begin, c_end) only; the sum goes to hf (float32 partial, [T][r]) when given, else to p.h as bf16.
-template <int NT, int TEAM>
+template <int NT, int TEAM, bool STAGED = false>
 __device__ __forceinline__ void xv_unit(const FactoredParams& p, float* redbuf, int k0, int c_begin, int c_end,
-                                        float* hf, int warp, int gid, int tig) {
+                                        float* hf, int warp, int gid, int tig, uint8_t* stage = nullptr) {
     const int N = p.N, T = p.T;
     const int g = k0 >> 7;
     const size_t rowb = static_cast<size_t>(N >> 1);
@@ -169,16 +199,14 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float* redbuf, 
     float acc[2][NT][4];             // only [0] is used; [1] stays zero so that the shared reducer applies
     zero_acc<NT>(acc);
     const int nchunks = c_end;
-    XvRegs<NT> cur, nxt;             // one chunk in flight while the previous one is multiplied
-    if (c_begin + warp < nchunks) xv_load<NT>(cur, p, row0, row1, g, ((c_begin + warp) << 7) + tig * 32, gid);
-    for (int c = c_begin + warp; c < nchunks; c += TEAM) {
-        const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
-        if (c + TEAM < nchunks) xv_load<NT>(nxt, p, row0, row1, g, ((c + TEAM) << 7) + tig * 32, gid);
-        const uint32_t cw0[4] = {cur.q0.x, cur.q0.y, cur.q0.z, cur.q0.w};
-        const uint32_t cw1[4] = {cur.q1.x, cur.q1.y, cur.q1.z, cur.q1.w};
-        const uint32_t sw[16] = {cur.s[0].x, cur.s[0].y, cur.s[0].z, cur.s[0].w, cur.s[1].x, cur.s[1].y, cur.s[1].z, cur.s[1].w,
-                                 cur.s[2].x, cur.s[2].y, cur.s[2].z, cur.s[2].w, cur.s[3].x, cur.s[3].y, cur.s[3].z, cur.s[3].w};
-        const uint32_t zw[8] = {cur.z[0].x, cur.z[0].y, cur.z[0].z, cur.z[0].w, cur.z[1].x, cur.z[1].y, cur.z[1].z, cur.z[1].w};
+    // one chunk of 128 columns: this thread's 32 columns of ranks gid and gid + 8 against the activations
+    auto chunk_mma = [&](const uint4& q0, const uint4& q1, const uint4 (&sv)[4], const uint4 (&zv)[2],
+                         const uint4 (&xv)[NT <= 2 ? NT : 1][4], int nb) {
+        const uint32_t cw0[4] = {q0.x, q0.y, q0.z, q0.w};
+        const uint32_t cw1[4] = {q1.x, q1.y, q1.z, q1.w};
+        const uint32_t sw[16] = {sv[0].x, sv[0].y, sv[0].z, sv[0].w, sv[1].x, sv[1].y, sv[1].z, sv[1].w,
+                                 sv[2].x, sv[2].y, sv[2].z, sv[2].w, sv[3].x, sv[3].y, sv[3].z, sv[3].w};
+        const uint32_t zw[8] = {zv[0].x, zv[0].y, zv[0].z, zv[0].w, zv[1].x, zv[1].y, zv[1].z, zv[1].w};
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {                  // 8 columns per packed word
             uint32_t e0[4], e1[4], a0[4], a1[4];
@@ -197,14 +225,82 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float* redbuf, 
             for (int nt = 0; nt < NT; ++nt) {
                 const int tok = nt * 8 + gid;
                 uint4 xq;
-                if (NT <= 2) xq = cur.x[NT <= 2 ? nt : 0][wi];
+                if (NT <= 2) xq = xv[NT <= 2 ? nt : 0][wi];
                 else xq = ldg16(p.x + static_cast<size_t>(min(tok, T - 1)) * N + nb + 8 * wi);
                 if (tok >= T) xq = make_uint4(0u, 0u, 0u, 0u);
                 mma_bf16(acc[0][nt], a0[0], a1[0], a0[1], a1[1], xq.x, xq.y);
                 mma_bf16(acc[0][nt], a0[2], a1[2], a0[3], a1[3], xq.z, xq.w);
             }
         }
-        if (c + TEAM < nchunks) cur = nxt;
+    };
+    if constexpr (STAGED && NT <= 2) {
+        // staged: every chunk of a wave is copied to shared memory at once (one round trip per wave)
+        const int lane = threadIdx.x & 31;
+        uint8_t* mine = stage + static_cast<size_t>(warp) * (FA_STAGE_CHUNKS * FA_STAGE_CHUNK_BYTES);
+        const uint32_t mine_s = smem_u32(mine);
+        auto load_x = [&](uint4 (&xv)[NT <= 2 ? NT : 1][4], int nb) {
+#pragma unroll
+            for (int nt = 0; nt < (NT <= 2 ? NT : 1); ++nt) {
+                const int tok = min(nt * 8 + gid, T - 1);
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) xv[nt][wi] = ldg16(p.x + static_cast<size_t>(tok) * N + nb + 8 * wi);
+            }
+        };
+        // chunks per wave: as many as the staging area holds, but the activations of a whole wave sit in registers
+        // (they are plain loads: issued late they would queue behind the copy stream of the main warps)
+        constexpr int CH = NT == 1 ? FA_STAGE_CHUNKS : FA_STAGE_CHUNKS / 2;
+        for (int cw = c_begin + warp; cw < nchunks; cw += TEAM * CH) {
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                const int c = cw + k * TEAM;
+                if (c < nchunks) {
+                    const int cols = c << 7;
+                    const uint32_t dst = mine_s + k * FA_STAGE_CHUNK_BYTES;
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int pid = lane + 32 * h2;   // 16 ranks x 4 pieces of 16 bytes
+                        fa_cp_async16(dst + pid * 16, p.vt + static_cast<size_t>(k0 + (pid >> 2)) * rowb + (cols >> 1) + (pid & 3) * 16);
+                    }
+                    if (lane < 16) fa_cp_async16(dst + 1024 + lane * 16, p.vs + static_cast<size_t>(g) * N + cols + 8 * lane);
+                    else if (lane < 24) fa_cp_async16(dst + 1280 + (lane - 16) * 16, p.vz + static_cast<size_t>(g) * N + cols + 16 * (lane - 16));
+                }
+            }
+            fa_cp_async_commit();
+            uint4 xw[CH][NT <= 2 ? NT : 1][4];
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                const int c = min(cw + k * TEAM, nchunks - 1);
+                load_x(xw[k], (c << 7) + tig * 32);
+            }
+            fa_cp_async_wait(0);
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < CH; ++k) {
+                const int c = cw + k * TEAM;
+                if (c < nchunks) {
+                    const int nb = (c << 7) + tig * 32;
+                    const uint8_t* src = mine + k * FA_STAGE_CHUNK_BYTES;
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(src + gid * 64 + tig * 16);
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(src + (gid + 8) * 64 + tig * 16);
+                    uint4 sv[4], zv[2];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sv[j] = *reinterpret_cast<const uint4*>(src + 1024 + tig * 64 + j * 16);
+                    zv[0] = *reinterpret_cast<const uint4*>(src + 1280 + tig * 32);
+                    zv[1] = *reinterpret_cast<const uint4*>(src + 1280 + tig * 32 + 16);
+                    chunk_mma(q0, q1, sv, zv, xw[k], nb);
+                }
+            }
+            __syncwarp();                                  // the next wave overwrites the staging area
+        }
+    } else {
+        XvRegs<NT> cur, nxt;             // one chunk in flight while the previous one is multiplied
+        if (c_begin + warp < nchunks) xv_load<NT>(cur, p, row0, row1, g, ((c_begin + warp) << 7) + tig * 32, gid);
+        for (int c = c_begin + warp; c < nchunks; c += TEAM) {
+            const int nb = (c << 7) + tig * 32;               // this thread's 32 columns
+            if (c + TEAM < nchunks) xv_load<NT>(nxt, p, row0, row1, g, ((c + TEAM) << 7) + tig * 32, gid);
+            chunk_mma(cur.q0, cur.q1, cur.s, cur.z, cur.x, nb);
+            if (c + TEAM < nchunks) cur = nxt;
+        }
     }
     // fixed-order sum over the team, 32 tokens at a time: redbuf[TEAM][32 tokens][16 ranks (+1 pad)]
     float (*red)[32][17] = reinterpret_cast<float (*)[32][17]>(redbuf);
@@ -311,6 +407,100 @@ __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2
 }
 
 // ---------------------------------------------------------------------------------------------
+// phase W through a shared-memory FIFO: the same 16-byte pieces as wx_block, but every thread copies
+// its own pieces with cp.async `stages - 1` blocks ahead (across the CTA's row blocks), so that
+// several items per thread are in flight without holding them in registers (x included: a plain load of x
+// would queue behind the copies and pay the loaded memory latency every item).  A thread reads back only what
+// it copied itself: no barrier guards the FIFO.  y goes to ybuf[row - row0][token].
+// ---------------------------------------------------------------------------------------------
+template <int NT>
+__device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[32][33], float* ybuf, const uint8_t* fifo,
+                                          int row0, int row1, int warp, int gid, int tig) {
+    constexpr int YS = 8 * NT + 1;
+    constexpr uint32_t STR = FA_THREADS * 16;               // distance between a thread's pieces of one item
+    constexpr int ITEM = fa_fifo_item(NT);
+    const int N = p.N, T = p.T, S = p.stages;
+    const int nblk = N >> 6;
+    const int cnt = (nblk - warp + FA_WARPS - 1) / FA_WARPS;        // 64-column blocks of this warp per row block
+    const int nb = (row1 - row0 + FA_ROWS - 1) / FA_ROWS;
+    const int total = nb * cnt;
+    const uint32_t fs = smem_u32(fifo) + threadIdx.x * 16;
+    const uint4* fr = reinterpret_cast<const uint4*>(fifo) + threadIdx.x;
+    const __nv_bfloat16* xrow[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xrow[nt] = p.x + static_cast<size_t>(min(nt * 8 + gid, T - 1)) * N + tig * 8;
+
+    int qi = 0, qb = 0;                                     // block column index and row block of the next item to issue
+    auto issue = [&](int q) {
+        if (q < total) {
+            const uint32_t sb = fs + (q % S) * ITEM;
+            const int col = (warp + FA_WARPS * qi) * 64 + tig * 8;
+            const int blk = row0 + qb * FA_ROWS;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr) {
+                    const int m = min(blk + mt * 16 + hr * 8 + gid, row1 - 1);     // rows past the slice: re-read the last one
+                    const __nv_bfloat16* src = p.w_b + static_cast<size_t>(m) * N + col;
+                    fa_cp_async16(sb + (mt * 4 + hr * 2) * STR, src);
+                    fa_cp_async16(sb + (mt * 4 + hr * 2 + 1) * STR, src + 32);
+                }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                fa_cp_async16(sb + (8 + 2 * nt) * STR, xrow[nt] + col - tig * 8);
+                fa_cp_async16(sb + (9 + 2 * nt) * STR, xrow[nt] + col - tig * 8 + 32);
+            }
+            if (++qi == cnt) {
+                qi = 0;
+                ++qb;
+            }
+        }
+        fa_cp_async_commit();                              // one group per call, empty past the end
+    };
+    for (int q = 0; q < S - 1; ++q) issue(q);
+
+    int q = 0;
+    for (int b = 0; b < nb; ++b) {
+        float acc[2][NT][4];
+        zero_acc<NT>(acc);
+        for (int i = 0; i < cnt; ++i, ++q) {
+            fa_cp_async_wait(S - 2);                        // item q has landed
+            uint4 A[2][2][2];
+            const uint4* slot = fr + static_cast<size_t>(q % S) * (ITEM / 16);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr)
+#pragma unroll
+                    for (int s2 = 0; s2 < 2; ++s2) A[mt][hr][s2] = slot[(mt * 4 + hr * 2 + s2) * FA_THREADS];
+            uint4 X[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int s2 = 0; s2 < 2; ++s2) X[nt][s2] = slot[(8 + 2 * nt + s2) * FA_THREADS];
+            issue(q + S - 1);                               // refills the slot read one iteration ago
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const bool live = nt * 8 + gid < T;
+#pragma unroll
+                for (int s2 = 0; s2 < 2; ++s2) {
+                    uint4 xq = X[nt][s2];
+                    if (!live) xq = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        mma_bf16(acc[mt][nt], A[mt][0][s2].x, A[mt][1][s2].x, A[mt][0][s2].y, A[mt][1][s2].y, xq.x, xq.y);
+                        mma_bf16(acc[mt][nt], A[mt][0][s2].z, A[mt][1][s2].z, A[mt][0][s2].w, A[mt][1][s2].w, xq.z, xq.w);
+                    }
+                }
+            }
+        }
+        float* yb = ybuf + static_cast<size_t>(b) * FA_ROWS * YS;
+        reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) { yb[row * YS + t] = s; });
+    }
+    fa_cp_async_wait(0);
+}
+
+// ---------------------------------------------------------------------------------------------
 // phase U: acc += sum_g us * (Ucode - uz)[rows, group g] h^T, one rank group per warp iteration.
 // ---------------------------------------------------------------------------------------------
 // SPLIT: h has been staged in shared memory (hs, bf16 [T][r + 8]); otherwise it is read from p.h (L2).
@@ -387,9 +577,13 @@ __device__ __forceinline__ int slice_start(int c, int G, int M, int unit_ctas, i
     return static_cast<int>(s < 0 ? 0 : (s > M ? M : s));
 }
 
-template <int NT, bool FUSE_WB>
+// FIFO: W_b streams through the shared-memory FIFO and the side warps stage their operands (T <= 16 and a
+// base weight only); a separate instantiation, so that the register-prefetch variant keeps its registers.
+template <int NT, bool FUSE_WB, bool FIFO = false>
 __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const FactoredParams p) {
-    extern __shared__ float fsmem[];
+    extern __shared__ float fsmem_all[];
+    const uint8_t* fifo = reinterpret_cast<const uint8_t*>(fsmem_all);                  // [stages][fa_fifo_item(NT)], may be empty
+    float* fsmem = fsmem_all + static_cast<size_t>(p.stages) * (fa_fifo_item(NT) / 4);
     float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(fsmem);
     constexpr int YS = 8 * NT + 1;                         // padded row stride of the y buffer
     constexpr bool SIDE = fa_side(NT);
@@ -409,15 +603,16 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         unsigned int done = 0;
         for (int u = G - 1 - c; u < n_units; u += G) {
             const int half = u & 1, mid = (nchunks + 1) >> 1;
-            xv_unit<NT, FA_SIDE_WARPS>(p, side_red, (u >> 1) * 16, half ? mid : 0, half ? nchunks : mid,
+            xv_unit<NT, FA_SIDE_WARPS, FIFO>(p, side_red, (u >> 1) * 16, half ? mid : 0, half ? nchunks : mid,
                                        reinterpret_cast<float*>(p.h) + static_cast<size_t>(half) * p.T * p.r,
-                                       warp - FA_WARPS, gid, tig);
+                                       warp - FA_WARPS, gid, tig,
+                                       FIFO ? reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * (8 * NT + 1))
+                                            : nullptr);                 // staged with the FIFO, from registers without
             ++done;
         }
-        if (done && threadIdx.x == FA_THREADS) {           // xv_unit ended with a barrier of the side warps
-            __threadfence();
-            atomicAdd(p.sync, done);
-        }
+        // xv_unit ended with a barrier of the side warps; the release orders their stores of h before the count.
+        // One fire-and-forget instruction: a fence and an atomic would be two more memory round trips under load.
+        if (done && threadIdx.x == FA_THREADS) red_release_gpu_add(p.sync, done);
         return;
     }
     if (!SIDE) {
@@ -433,7 +628,9 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     }
 
     // ---- phase W
-    if (FUSE_WB) {
+    if constexpr (FIFO) {
+        wx_stream<NT>(p, red, ybuf, fifo, row0, row1, warp, gid, tig);
+    } else if (FUSE_WB) {
         for (int blk = row0; blk < row1; blk += FA_ROWS) {
             float acc[2][NT][4];
             zero_acc<NT>(acc);

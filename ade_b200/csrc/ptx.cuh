@@ -226,6 +226,11 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
     return v;
 }
 
+// counter += v with release semantics at GPU scope, no return value: the issuing thread does not wait for it
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // packed pairs of float32 in one 64-bit register: sm_100 executes add / mul on both lanes in one
 // instruction, each lane rounded exactly like the scalar .rn operation
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
