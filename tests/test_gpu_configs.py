@@ -51,6 +51,25 @@ def test_config0_factored_q_proj():
     assert err0 > 2 * err
 
 
+@pytest.mark.parametrize("M,N,r,T", [(11008, 4096, 512, 1), (11008, 4096, 512, 8), (4096, 11008, 512, 8), (4096, 11008, 256, 16),
+                                     (11008, 4096, 1024, 3)])
+def test_factored_mlp_modules_long_streams(M, N, r, T):
+    """Decode sizes on the MLP shapes of configs 2-4: every CTA streams more than 400 KB of W_b, which selects
+    the shared-memory FIFO variant of the factored kernel (d_i = 11008 also needs several staging waves)."""
+    tp = synth.random_packed(M, N, r, 31 * T + r)
+    W_b = synth.base_weight(M, N, 7)
+    x = synth.activations(T, N, 8)
+    p4 = kernels.pack_int4(tp, device=DEV)
+    y = kernels.factored_forward(x.to(DEV), p4, weight=W_b.to(DEV))
+    y2 = kernels.factored_forward(x.to(DEV), p4, weight=W_b.to(DEV))
+    torch.cuda.synchronize()
+    assert kernels.factored_status(DEV, T, r) == 0
+    assert torch.equal(y, y2)                      # deterministic, and the sync words re-armed themselves
+    ref = O.factored_apply(_bits(x), _bits(W_b), O.packed_from_torch(tp))
+    err, cos = O.parity(y.float().cpu().numpy(), ref)
+    assert err <= 1e-2 and cos >= 0.9999, (err, cos)
+
+
 @pytest.mark.parametrize("name,M,N", [("gate", 11008, 4096), ("down", 4096, 11008)])
 def test_config1_reconstructed_mlp(name, M, N):
     """Config 1: Llama-2-7B MLP deltas, r = 512, X 2048 x d_i, reconstructed path."""
