@@ -55,7 +55,7 @@ def factored_bytes(M, N, r, T, fused):
 
 WORK_OPS = sum(delta_ops(M, N, RANK) for _, M, N in MODULES)
 # dram__bytes_read.sum + dram__bytes_write.sum of one reconstruction launch on gate_proj, from the ncu capture
-# summarised in profiles/recon_kernel_gate_proj_r512.md (95.5 MB + 51.6 MB; part of W' is still in L2 at exit)
+# summarised in profiles/recon_strip_kernel_gate_proj_r512.md (95.5 MB + 51.6 MB; part of W' is still in L2 at exit)
 RECON_TRAFFIC_BYTES = 147.1e6
 
 
