@@ -150,6 +150,7 @@ template <int NT, bool FUSE>
 int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
     size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
     p.stages = 0;
+    p.upf = 0;
     // Decode sizes with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than registers allow).
     // Short streams (a 4096 x 4096 module is 227 KB per CTA) are faster with the register prefetch: the deep
     // FIFO raises the loaded memory latency, and the h hand-over pays it several times.
@@ -158,6 +159,13 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
         const size_t room = (static_cast<size_t>(kMaxSmem) - smem) / ade::fa_fifo_item(NT);
         p.stages = room >= 2 ? static_cast<int>(room < static_cast<size_t>(ade::FA_FIFO_MAX) ? room : ade::FA_FIFO_MAX) : 0;
         smem += static_cast<size_t>(p.stages) * ade::fa_fifo_item(NT);
+    }
+    // operands of the first phase-U items are prefetched into shared memory: the drained FIFO, or an area of their own
+    if (p.stages >= 2) {
+        p.upf = ade::FA_UPF;
+    } else if (smem + static_cast<size_t>(ade::FA_UPF) * ade::FA_UPF_ITEM <= static_cast<size_t>(kMaxSmem)) {
+        p.upf = ade::FA_UPF;
+        smem += static_cast<size_t>(ade::FA_UPF) * ade::FA_UPF_ITEM;
     }
     if constexpr (FUSE && ade::fa_side(NT)) {
         if (p.stages >= 2) {
@@ -176,15 +184,12 @@ int launch_factored(const ade::FactoredParams& p, int grid, cudaStream_t st) {
 
 template <int NT>
 bool optin_factored() {
-    const int smem = ade::fa_side(NT) ? kMaxSmem
-                                      : static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, 0, ADE_B200_MAX_RANK));
     if constexpr (ade::fa_side(NT)) {
         if (!cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)))
             return false;
     }
-    return cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) &&
-           cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(ade::factored_smem_bytes(NT, kMaxRowsCap, NT <= 2 ? 16 : 0, ADE_B200_MAX_RANK))));
+    return cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)) &&
+           cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
 }
 
 // ---- scratch of ade_b200_factored_static: lives in the library image, one copy per GPU that loads it.

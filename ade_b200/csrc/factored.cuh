@@ -62,6 +62,7 @@ struct FactoredParams {
     int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
     int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
     int stages;                    // depth of the shared-memory FIFO that streams W_b (0: register prefetch)
+    int upf;                       // phase-U items per warp whose operands are prefetched into shared memory (0..FA_UPF)
 };
 
 // Side warps stage the V codes, scales and zero-points of up to FA_STAGE_CHUNKS chunks of 128 columns per warp
@@ -501,45 +502,85 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
 }
 
 // ---------------------------------------------------------------------------------------------
-// phase U: acc += sum_g us * (Ucode - uz)[rows, group g] h^T, one rank group per warp iteration.
+// phase U: acc += sum_g us * (Ucode - uz)[rows, group g] h^T.  A work item is one m16 tile of the 32-row block
+// times one rank group; item j = 2 g + tile goes to warp j % 8, so four warps already share a block at r = 256.
+// The operands of a warp's first FA_UPF items (over all its row blocks) are copied to shared memory before the
+// grid-wide wait for h (they do not depend on it), which takes their memory round trip off the path behind it.
 // ---------------------------------------------------------------------------------------------
+constexpr int FA_UPF = 4;
+constexpr int FA_UPF_ITEM = FA_THREADS * (2 * 16 + 2 * 8);     // per item and thread: two 16-byte code pieces, two (zero, scale) word pairs
+__device__ __forceinline__ void fa_cp_async4(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* ustage, int row0, int row1, int warp, int gid,
+                                            int tig) {
+    const int ng = p.r >> 7, nitems = 2 * ng;
+    const size_t rowb = static_cast<size_t>(p.r >> 1);
+    const uint32_t us_s = smem_u32(ustage);
+    int k = 0;
+    for (int blk = row0; blk < row1 && k < p.upf; blk += FA_ROWS)
+        for (int j = warp; j < nitems && k < p.upf; j += FA_WARPS, ++k) {
+            const int mt = j & 1, g = j >> 1;
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int m = min(blk + mt * 16 + hr * 8 + gid, row1 - 1);
+                const size_t e = static_cast<size_t>(m) * ng + g;
+                const uint32_t base = us_s + k * FA_UPF_ITEM;
+                fa_cp_async16(base + (hr * FA_THREADS + threadIdx.x) * 16, p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
+                const uint32_t sc = base + 2 * FA_THREADS * 16 + (hr * FA_THREADS + threadIdx.x) * 8;
+                fa_cp_async4(sc, p.uz + (e & ~static_cast<size_t>(3)));                 // the aligned word that holds the zero-point
+                fa_cp_async4(sc + 4, p.us + (e & ~static_cast<size_t>(1)));             // ... and the one that holds the scale
+            }
+        }
+    fa_cp_async_commit();
+}
+
 // SPLIT: h has been staged in shared memory (hs, bf16 [T][r + 8]); otherwise it is read from p.h (L2).
+// k: running index of this warp's items over the blocks (the first p.upf were prefetched).
 template <int NT, bool SPLIT>
 __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
-                                         const __nv_bfloat16* hs, int warp, int gid, int tig) {
+                                         const __nv_bfloat16* hs, const uint8_t* ustage, int& k, int warp, int gid, int tig) {
     const int T = p.T, r = p.r;
     const int ng = r >> 7;
     const size_t rowb = static_cast<size_t>(r >> 1);
-    for (int g = warp; g < ng; g += FA_WARPS) {
-        uint32_t a[2][2][16];        // [m16 tile][row gid / gid+8][pair]: (code - zero) as bf16x2
-        float su[2][2];
+    for (int j = warp; j < 2 * ng; j += FA_WARPS, ++k) {
+        const int mt = j & 1, g = j >> 1;
+        uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
+        float su[2];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int hr = 0; hr < 2; ++hr) {
-                const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
-                const uint4 q = ldg16_stream(p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
-                const uint32_t z = p.uz[static_cast<size_t>(m) * ng + g];
-                const uint32_t zz = kBf2_128 | z | (z << 16);
-                su[mt][hr] = bf16_bits_to_f32(p.us[static_cast<size_t>(m) * ng + g]);
-                const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    uint32_t e[4];
-                    unpack8_bf16(cw[wi], e);
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) a[mt][hr][4 * wi + q4] = bf2_sub(e[q4], zz);
-                }
+        for (int hr = 0; hr < 2; ++hr) {
+            const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
+            const size_t e = static_cast<size_t>(m) * ng + g;
+            uint4 q;
+            uint32_t z, sbits;
+            if (k < p.upf) {
+                const uint8_t* base = ustage + static_cast<size_t>(k) * FA_UPF_ITEM;
+                q = *reinterpret_cast<const uint4*>(base + (hr * FA_THREADS + threadIdx.x) * 16);
+                const uint2 w = *reinterpret_cast<const uint2*>(base + 2 * FA_THREADS * 16 + (hr * FA_THREADS + threadIdx.x) * 8);
+                z = (w.x >> (8 * static_cast<uint32_t>(e & 3))) & 0xFFu;
+                sbits = (w.y >> (16 * static_cast<uint32_t>(e & 1))) & 0xFFFFu;
+            } else {
+                q = ldg16_stream(p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
+                z = p.uz[e];
+                sbits = p.us[e];
             }
+            const uint32_t zz = kBf2_128 | z | (z << 16);
+            su[hr] = bf16_bits_to_f32(static_cast<uint16_t>(sbits));
+            const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                uint32_t ev[4];
+                unpack8_bf16(cw[wi], ev);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) a[hr][4 * wi + q4] = bf2_sub(ev[q4], zz);
+            }
+        }
         const int kb = g * 128 + tig * 32;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const int tok = nt * 8 + gid;
-            float pa[2][4];
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) pa[mt][i] = 0.f;
+            float pa[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 uint4 hq = make_uint4(0u, 0u, 0u, 0u);
@@ -547,20 +588,20 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
                     if (SPLIT) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
                     else hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
                 }
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    mma_bf16(pa[mt], a[mt][0][4 * wi], a[mt][1][4 * wi], a[mt][0][4 * wi + 1], a[mt][1][4 * wi + 1],
-                             hq.x, hq.y);
-                    mma_bf16(pa[mt], a[mt][0][4 * wi + 2], a[mt][1][4 * wi + 2], a[mt][0][4 * wi + 3],
-                             a[mt][1][4 * wi + 3], hq.z, hq.w);
-                }
+                mma_bf16(pa, a[0][4 * wi], a[1][4 * wi], a[0][4 * wi + 1], a[1][4 * wi + 1], hq.x, hq.y);
+                mma_bf16(pa, a[0][4 * wi + 2], a[1][4 * wi + 2], a[0][4 * wi + 3], a[1][4 * wi + 3], hq.z, hq.w);
             }
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {              // one rescale per group
-                acc[mt][nt][0] += su[mt][0] * pa[mt][0];
-                acc[mt][nt][1] += su[mt][0] * pa[mt][1];
-                acc[mt][nt][2] += su[mt][1] * pa[mt][2];
-                acc[mt][nt][3] += su[mt][1] * pa[mt][3];
+            // one rescale per group; mt selects the accumulator tile
+            if (mt == 0) {
+                acc[0][nt][0] += su[0] * pa[0];
+                acc[0][nt][1] += su[0] * pa[1];
+                acc[0][nt][2] += su[1] * pa[2];
+                acc[0][nt][3] += su[1] * pa[3];
+            } else {
+                acc[1][nt][0] += su[0] * pa[0];
+                acc[1][nt][1] += su[0] * pa[1];
+                acc[1][nt][2] += su[1] * pa[2];
+                acc[1][nt][3] += su[1] * pa[3];
             }
         }
     }
@@ -641,6 +682,12 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         }
     }
 
+    // operands of the first phase-U items: in flight while this CTA waits for h.  The stream variant reuses its
+    // FIFO (drained by now), the others have an area of their own behind the h tile.
+    uint8_t* ustage = FIFO ? const_cast<uint8_t*>(fifo)
+                           : reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * YS) + (SIDE ? fa_side_region(p.T, p.r) : 0);
+    if (p.upf > 0) uh_prefetch(p, ustage, row0, row1, warp, gid, tig);
+
     // ---- wait for every h unit (bounded; on expiry record a status and carry on)
     if (threadIdx.x == 0) {
         const long long t0 = clock64();
@@ -674,10 +721,12 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     }
 
     // ---- phase U and store
+    if (p.upf > 0) fa_cp_async_wait(0);                    // every thread reads back only its own copies
+    int uk = 0;
     for (int blk = row0; blk < row1; blk += FA_ROWS) {
         float acc[2][NT][4];
         zero_acc<NT>(acc);
-        uh_block<NT, SIDE>(p, acc, blk, row1, hs, warp, gid, tig);
+        uh_block<NT, SIDE>(p, acc, blk, row1, hs, ustage, uk, warp, gid, tig);
         const float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
         const int T = p.T, M = p.M;
         const __nv_bfloat16* yd = p.y_dense;
