@@ -52,8 +52,10 @@ int device_info(const DeviceInfo** out) {
             const int smem = kMaxSmem;
             if (!cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
-                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
-                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
                 return ADE_ERR_CUDA;
             if (!optin_factored<1>() || !optin_factored<2>() || !optin_factored<4>() || !optin_factored<8>() ||
                 !optin_factored<16>())
@@ -367,8 +369,8 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     const int ng = d->r / ADE_B200_GROUP;
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;
-    if (ng <= ade::RS_MAX_GROUPS) {
-        // ranks up to 512: the strip-resident kernel, all global traffic through tensor maps
+    if (ng <= ade::RS_MAX_GROUPS && ade::recon_strip_smem_bytes(ng) <= static_cast<size_t>(kMaxSmem)) {
+        // ranks up to 1024: the strip-resident kernel, all global traffic through tensor maps
         if (!load_encode_tiled()) return ADE_ERR_CUDA;
         ade::ReconMaps maps;
         const uint64_t M = static_cast<uint64_t>(d->M), N = static_cast<uint64_t>(d->N), rb = static_cast<uint64_t>(d->r / 2);
@@ -378,10 +380,14 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
             !make_map_2d(&maps.vq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->vq, rb, N, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE))
             return ADE_ERR_CUDA;
         const size_t smem = ade::recon_strip_smem_bytes(ng);
-        if (dbg_acc)
-            ade::recon_strip_kernel<true><<<grid, ade::RS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p, maps);
-        else
-            ade::recon_strip_kernel<false><<<grid, ade::RS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p, maps);
+        const cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (ng > 4) {
+            if (dbg_acc) ade::recon_strip_kernel<true, true><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);
+            else ade::recon_strip_kernel<false, true><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);
+        } else {
+            if (dbg_acc) ade::recon_strip_kernel<true, false><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);
+            else ade::recon_strip_kernel<false, false><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);
+        }
         return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
     }
     if (ade::recon_smem_bytes(ng) > static_cast<size_t>(kMaxSmem)) return ADE_ERR_SHAPE;    // rank too large for one CTA's scale tables

@@ -1,4 +1,4 @@
-// Reconstructed application for ranks up to 512 (at most four groups of 128): same arithmetic, same
+// Reconstructed application for ranks up to 1024 (at most eight groups of 128): same arithmetic, same
 // roundings and same tensor-core contraction as recon_kernel (recon.cuh), organised around a resident
 // strip of the U operand.
 //
@@ -26,21 +26,18 @@
 
 namespace ade {
 
-constexpr int RS_MAX_GROUPS = 4;
+constexpr int RS_MAX_GROUPS = 8;                         // ranks up to 1024
 constexpr int RS_EPI_WARPS = 16;
 constexpr int RS_MMA_WARP = 20;
 constexpr int RS_LOAD_WARP = 21;
 constexpr int RS_SCALE_WARP = 22;
 constexpr int RS_THREADS = 23 * 32;
-constexpr int RS_B_STAGES = 3;                           // int8 V tiles in flight
-constexpr int RS_RAW_DEPTH = 4;                          // packed items in flight
 constexpr int RS_OPER_BYTES = RC_TILE * 128;             // one int8 operand tile of one group
 constexpr int RS_RAW_CODES = RC_TILE * 64;               // 128 rows x 64 bytes of nibbles
 constexpr int RS_RAW_SLOT = RS_RAW_CODES + 256;          // + 128 zero-points, padded
 constexpr int RS_ACC_STAGES = 4;                        // 128-column accumulators in tensor memory (all 512 columns)
 constexpr int RS_TMEM_COLS = RS_ACC_STAGES * RC_TILE;
 constexpr int RS_BOX_BYTES = 32 * 64;                    // a warp's 32 x 32 bf16 box
-constexpr int RS_WB_BYTES = RS_EPI_WARPS * 2 * RS_BOX_BYTES;
 // scale tables of one tile, per group: us of the 128 rows, then vs of the 128 columns, as float32
 constexpr int RS_SC_BYTES = 512 + 512;
 
@@ -51,23 +48,37 @@ struct ReconMaps {
     CUtensorMap vq;     // (N, r/2) bytes, box 128 rows x 64 bytes
 };
 
-// barrier indices (8 bytes each)
-constexpr int RS_BAR_RAW_FULL = 0;
-constexpr int RS_BAR_RAW_EMPTY = RS_BAR_RAW_FULL + RS_RAW_DEPTH;
-constexpr int RS_BAR_B_FULL = RS_BAR_RAW_EMPTY + RS_RAW_DEPTH;
-constexpr int RS_BAR_B_EMPTY = RS_BAR_B_FULL + RS_B_STAGES;
-constexpr int RS_BAR_A_FULL = RS_BAR_B_EMPTY + RS_B_STAGES;
-constexpr int RS_BAR_A_FREE = RS_BAR_A_FULL + RS_MAX_GROUPS;
-constexpr int RS_BAR_TFULL = RS_BAR_A_FREE + 1;
-constexpr int RS_BAR_TEMPTY = RS_BAR_TFULL + RS_ACC_STAGES;
-constexpr int RS_BAR_SC_FULL = RS_BAR_TEMPTY + RS_ACC_STAGES;
-constexpr int RS_BAR_SC_EMPTY = RS_BAR_SC_FULL + 2;
-constexpr int RS_BAR_WB = RS_BAR_SC_EMPTY + 2;
-constexpr int RS_BAR_COUNT = RS_BAR_WB + 2 * RS_EPI_WARPS;
+// Ring depths and barrier indices.  BIG (five to eight groups): the resident strip takes up to 128 KB, so the
+// rings shrink to two V stages, two raw slots and one box buffer per warp (measured: ring depth is not what
+// limits this kernel).
+template <bool BIG>
+struct RsCfg {
+    static constexpr int GROUPS = BIG ? 8 : 4;           // resident groups at most
+    static constexpr int B_STAGES = BIG ? 2 : 3;         // int8 V tiles in flight
+    static constexpr int RAW_DEPTH = BIG ? 2 : 4;        // packed items in flight
+    static constexpr int WB_BUFS = BIG ? 1 : 2;          // box buffers per epilogue warp
+    static constexpr int WB_BYTES = RS_EPI_WARPS * WB_BUFS * RS_BOX_BYTES;
+    // barrier indices (8 bytes each)
+    static constexpr int BAR_RAW_FULL = 0;
+    static constexpr int BAR_RAW_EMPTY = BAR_RAW_FULL + RAW_DEPTH;
+    static constexpr int BAR_B_FULL = BAR_RAW_EMPTY + RAW_DEPTH;
+    static constexpr int BAR_B_EMPTY = BAR_B_FULL + B_STAGES;
+    static constexpr int BAR_A_FULL = BAR_B_EMPTY + B_STAGES;
+    static constexpr int BAR_A_FREE = BAR_A_FULL + GROUPS;
+    static constexpr int BAR_TFULL = BAR_A_FREE + 1;
+    static constexpr int BAR_TEMPTY = BAR_TFULL + RS_ACC_STAGES;
+    static constexpr int BAR_SC_FULL = BAR_TEMPTY + RS_ACC_STAGES;
+    static constexpr int BAR_SC_EMPTY = BAR_SC_FULL + 2;
+    static constexpr int BAR_WB = BAR_SC_EMPTY + 2;
+    static constexpr int BAR_COUNT = BAR_WB + WB_BUFS * RS_EPI_WARPS;
+    static constexpr size_t smem_bytes(int ng) {
+        return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(B_STAGES) * RS_OPER_BYTES +
+               WB_BYTES + static_cast<size_t>(RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + BAR_COUNT * 8 + 16;
+    }
+};
 
 __host__ __device__ inline size_t recon_strip_smem_bytes(int ng) {
-    return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(RS_B_STAGES) * RS_OPER_BYTES +
-           RS_WB_BYTES + static_cast<size_t>(RS_RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + RS_BAR_COUNT * 8 + 16;
+    return ng > 4 ? RsCfg<true>::smem_bytes(ng) : RsCfg<false>::smem_bytes(ng);
 }
 
 // As unpack_store (recon.cuh), with the tile given by its shared-window address.
@@ -88,44 +99,45 @@ __device__ __forceinline__ void unpack_store_s(uint32_t tile, int row, int c, ui
     sts16(rp + (((2 * c + 1) ^ sw) << 4), make_uint4(o[4], o[5], o[6], o[7]));
 }
 
-template <bool DBG>
+template <bool DBG, bool BIG>
 __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconParams p, const __grid_constant__ ReconMaps maps) {
+    using C = RsCfg<BIG>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
     const uint32_t base = (raw0 + 1023u) & ~1023u;
     const int ng = p.r >> 7;
     const uint32_t a_res = base;                                          // [ng][128][128] int8, resident strip of U
-    const uint32_t b_st = a_res + ng * RS_OPER_BYTES;                     // [RS_B_STAGES][128][128] int8
-    const uint32_t wbuf = b_st + RS_B_STAGES * RS_OPER_BYTES;             // [16 warps][2][32][64 B]
-    const uint32_t rawr = wbuf + RS_WB_BYTES;                             // [RS_RAW_DEPTH][RS_RAW_SLOT]
-    const uint32_t scf = rawr + RS_RAW_DEPTH * RS_RAW_SLOT;               // [2][ng][RS_SC_BYTES] scale tables
+    const uint32_t b_st = a_res + ng * RS_OPER_BYTES;                     // [C::B_STAGES][128][128] int8
+    const uint32_t wbuf = b_st + C::B_STAGES * RS_OPER_BYTES;             // [16 warps][2][32][64 B]
+    const uint32_t rawr = wbuf + C::WB_BYTES;                             // [C::RAW_DEPTH][RS_RAW_SLOT]
+    const uint32_t scf = rawr + C::RAW_DEPTH * RS_RAW_SLOT;               // [2][ng][RS_SC_BYTES] scale tables
     const uint32_t bars = scf + ng * RS_SC_BYTES * 2;
     uint8_t* gen = smem_raw + (bars - raw0);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + RS_BAR_COUNT * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_COUNT * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RS_RAW_DEPTH; ++i) {
-            mbar_init(bar(RS_BAR_RAW_FULL + i), 1);
-            mbar_init(bar(RS_BAR_RAW_EMPTY + i), 4);
+        for (int i = 0; i < C::RAW_DEPTH; ++i) {
+            mbar_init(bar(C::BAR_RAW_FULL + i), 1);
+            mbar_init(bar(C::BAR_RAW_EMPTY + i), 4);
         }
-        for (int i = 0; i < RS_B_STAGES; ++i) {
-            mbar_init(bar(RS_BAR_B_FULL + i), 4);
-            mbar_init(bar(RS_BAR_B_EMPTY + i), 1);
+        for (int i = 0; i < C::B_STAGES; ++i) {
+            mbar_init(bar(C::BAR_B_FULL + i), 4);
+            mbar_init(bar(C::BAR_B_EMPTY + i), 1);
         }
-        for (int i = 0; i < RS_MAX_GROUPS; ++i) mbar_init(bar(RS_BAR_A_FULL + i), 4);
-        mbar_init(bar(RS_BAR_A_FREE), 1);
+        for (int i = 0; i < C::GROUPS; ++i) mbar_init(bar(C::BAR_A_FULL + i), 4);
+        mbar_init(bar(C::BAR_A_FREE), 1);
         for (int i = 0; i < RS_ACC_STAGES; ++i) {
-            mbar_init(bar(RS_BAR_TFULL + i), 1);
-            mbar_init(bar(RS_BAR_TEMPTY + i), RS_EPI_WARPS);
+            mbar_init(bar(C::BAR_TFULL + i), 1);
+            mbar_init(bar(C::BAR_TEMPTY + i), RS_EPI_WARPS);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(RS_BAR_SC_FULL + i), 1);
-            mbar_init(bar(RS_BAR_SC_EMPTY + i), RS_EPI_WARPS);
+            mbar_init(bar(C::BAR_SC_FULL + i), 1);
+            mbar_init(bar(C::BAR_SC_EMPTY + i), RS_EPI_WARPS);
         }
-        for (int i = 0; i < 2 * RS_EPI_WARPS; ++i) mbar_init(bar(RS_BAR_WB + i), 1);
+        for (int i = 0; i < C::WB_BUFS * RS_EPI_WARPS; ++i) mbar_init(bar(C::BAR_WB + i), 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -148,7 +160,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         const int q = warp & 3, hh = warp >> 2;
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * 32;
-        const uint32_t box0 = wbuf + warp * (2 * RS_BOX_BYTES);
+        const uint32_t box0 = wbuf + warp * (C::WB_BUFS * RS_BOX_BYTES);
         const uint32_t own = lane * 64;                   // this thread's row of the box
         const int swz = (lane >> 1) & 3;                  // 64-byte swizzle: 16-byte chunk index ^ bits 7-8 of the address
         uint32_t magic4[4];
@@ -163,7 +175,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         __syncwarp();
         if (lane == 0) {
 #pragma unroll
-            for (int st = 0; st < RS_ACC_STAGES; ++st) mbar_arrive(bar(RS_BAR_TEMPTY + st));
+            for (int st = 0; st < RS_ACC_STAGES; ++st) mbar_arrive(bar(C::BAR_TEMPTY + st));
             prefetch_tensormap(&maps.wb);
             prefetch_tensormap(&maps.out);
         }
@@ -175,13 +187,15 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             const int m = m0 + row;
             const bool live = m < p.M;
             const uint32_t b = j & 1, jph = (j >> 1) & 1;
-            const uint32_t box = box0 + b * RS_BOX_BYTES;
+            const uint32_t wbb = C::WB_BUFS == 2 ? b : 0, wph = C::WB_BUFS == 2 ? jph : static_cast<uint32_t>(j & 1);
+            const uint32_t box = box0 + wbb * RS_BOX_BYTES;
+            const uint32_t wbar = bar(C::BAR_WB + C::WB_BUFS * warp + wbb);
             if (lane == 0) {
-                bulk_wait_group_read<1>();               // the store that last read this box buffer is done with it
-                mbar_arrive_expect_tx(bar(RS_BAR_WB + 2 * warp + b), RS_BOX_BYTES);
-                tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, bar(RS_BAR_WB + 2 * warp + b));
+                bulk_wait_group_read<C::WB_BUFS - 1>();  // the store that last read this box buffer is done with it
+                mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
+                tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
             }
-            wait_bounded(bar(RS_BAR_SC_FULL + b), jph, abort_flag, p.status, 5);
+            wait_bounded(bar(C::BAR_SC_FULL + b), jph, abort_flag, p.status, 5);
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);          // this tile's tables
 
             uint64_t acc[16];
@@ -191,7 +205,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                wait_bounded(bar(RS_BAR_TFULL + a), aph, abort_flag, p.status, 3);
+                wait_bounded(bar(C::BAR_TFULL + a), aph, abort_flag, p.status, 3);
                 tc_fence_after();
                 const uint32_t scg = sct + g * RS_SC_BYTES;
                 const float u = __uint_as_float(lds4(scg + row * 4));
@@ -232,11 +246,11 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 tmem_st_wait();                          // accumulator stage re-armed: hand it back
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(RS_BAR_TEMPTY + a));
+                if (lane == 0) mbar_arrive(bar(C::BAR_TEMPTY + a));
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(RS_BAR_SC_EMPTY + b));             // this warp is done with the scale tables
-            wait_bounded(bar(RS_BAR_WB + 2 * warp + b), jph, abort_flag, p.status, 6);
+            if (lane == 0) mbar_arrive(bar(C::BAR_SC_EMPTY + b));             // this warp is done with the scale tables
+            wait_bounded(wbar, wph, abort_flag, p.status, 6);
             uint4 wv4[4];                                // 8 columns per 16-byte chunk
 #pragma unroll
             for (int c = 0; c < 4; ++c) wv4[c] = lds16(box + own + ((c ^ swz) << 4));
@@ -268,7 +282,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         const int c = pt & 3, rbase = pt >> 2;
         uint32_t ri = 0, bi = 0, sk = 0;
         int cur_strip = -1;
-        uint32_t za_pack[4] = {0, 0, 0, 0};               // zero-points of this thread's four U rows, one byte per group
+        uint64_t za_pack[4] = {0, 0, 0, 0};               // zero-points of this thread's four U rows, one byte per group
         for (int tile = t_begin; tile < t_end; ++tile) {
             const int strip = tile / tiles_n;
             if (strip != cur_strip) {
@@ -277,33 +291,33 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int m = m0 + rbase + 32 * i;
-                    uint32_t z = 0;
+                    uint64_t z = 0;
                     if (m < p.M)
-                        for (int g = 0; g < ng; ++g) z |= static_cast<uint32_t>(p.uz[static_cast<size_t>(m) * ng + g]) << (8 * g);
+                        for (int g = 0; g < ng; ++g) z |= static_cast<uint64_t>(p.uz[static_cast<size_t>(m) * ng + g]) << (8 * g);
                     za_pack[i] = z;
                 }
-                if (sk > 0) wait_bounded(bar(RS_BAR_A_FREE), (sk - 1) & 1, abort_flag, p.status, 7);   // old strip's MMAs retired
+                if (sk > 0) wait_bounded(bar(C::BAR_A_FREE), (sk - 1) & 1, abort_flag, p.status, 7);   // old strip's MMAs retired
                 for (int g = 0; g < ng; ++g, ++ri) {
-                    const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
-                    wait_bounded(bar(RS_BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                    const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
+                    wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
                     const uint32_t rs = rawr + slot * RS_RAW_SLOT;
                     uint4 qa[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) qa[i] = lds16(rs + (rbase + 32 * i) * 64 + c * 16);
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(RS_BAR_RAW_EMPTY + slot));
+                    if (lane == 0) mbar_arrive(bar(C::BAR_RAW_EMPTY + slot));
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        unpack_store_s(a_res + g * RS_OPER_BYTES, rbase + 32 * i, c, qa[i], (za_pack[i] >> (8 * g)) & 0xFFu);
+                        unpack_store_s(a_res + g * RS_OPER_BYTES, rbase + 32 * i, c, qa[i], static_cast<uint32_t>(za_pack[i] >> (8 * g)) & 0xFFu);
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(RS_BAR_A_FULL + g));
+                    if (lane == 0) mbar_arrive(bar(C::BAR_A_FULL + g));
                 }
                 ++sk;
             }
             for (int g = 0; g < ng; ++g, ++ri, ++bi) {
-                const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
-                wait_bounded(bar(RS_BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
+                wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
                 const uint32_t rs = rawr + slot * RS_RAW_SLOT;
                 uint4 qb[4];
                 uint32_t zb[4];
@@ -313,14 +327,14 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     zb[i] = lds1(rs + RS_RAW_CODES + rbase + 32 * i);
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(RS_BAR_RAW_EMPTY + slot));
-                const uint32_t s = bi % RS_B_STAGES, bph = (bi / RS_B_STAGES) & 1;
-                wait_bounded(bar(RS_BAR_B_EMPTY + s), bph ^ 1, abort_flag, p.status, 2);
+                if (lane == 0) mbar_arrive(bar(C::BAR_RAW_EMPTY + slot));
+                const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
+                wait_bounded(bar(C::BAR_B_EMPTY + s), bph ^ 1, abort_flag, p.status, 2);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) unpack_store_s(b_st + s * RS_OPER_BYTES, rbase + 32 * i, c, qb[i], zb[i]);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(RS_BAR_B_FULL + s));
+                if (lane == 0) mbar_arrive(bar(C::BAR_B_FULL + s));
             }
         }
     } else if (warp == RS_MMA_WARP) {
@@ -332,19 +346,19 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 const bool last = tile == t_end - 1 || (tile + 1) % tiles_n == 0;
                 for (int g = 0; g < ng; ++g, ++it, ++bi) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                    const uint32_t s = bi % RS_B_STAGES, bph = (bi / RS_B_STAGES) & 1;
-                    wait_bounded(bar(RS_BAR_TEMPTY + a), aph, abort_flag, p.status, 4);
-                    wait_bounded(bar(RS_BAR_B_FULL + s), bph, abort_flag, p.status, 1);
-                    if (first) wait_bounded(bar(RS_BAR_A_FULL + g), k & 1, abort_flag, p.status, 9);
+                    const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
+                    wait_bounded(bar(C::BAR_TEMPTY + a), aph, abort_flag, p.status, 4);
+                    wait_bounded(bar(C::BAR_B_FULL + s), bph, abort_flag, p.status, 1);
+                    if (first) wait_bounded(bar(C::BAR_A_FULL + g), k & 1, abort_flag, p.status, 9);
                     tc_fence_after();
                     const uint64_t ad = smem_desc_k_sw128(a_res + g * RS_OPER_BYTES);
                     const uint64_t bd = smem_desc_k_sw128(b_st + s * RS_OPER_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * kk, bd + 2 * kk, RC_IDESC, 1u);
-                    tc_commit(bar(RS_BAR_B_EMPTY + s));
-                    tc_commit(bar(RS_BAR_TFULL + a));
-                    if (last && g == ng - 1) tc_commit(bar(RS_BAR_A_FREE));    // the strip of U may be overwritten
+                    tc_commit(bar(C::BAR_B_EMPTY + s));
+                    tc_commit(bar(C::BAR_TFULL + a));
+                    if (last && g == ng - 1) tc_commit(bar(C::BAR_A_FREE));    // the strip of U may be overwritten
                 }
                 if (last) ++k;
             }
@@ -362,19 +376,19 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 if (strip != cur_strip) {
                     cur_strip = strip;
                     for (int g = 0; g < ng; ++g, ++ri) {
-                        const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
-                        wait_bounded(bar(RS_BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
-                        mbar_arrive_expect_tx(bar(RS_BAR_RAW_FULL + slot), RS_RAW_CODES);
-                        tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.uq, g * 64, strip << 7, bar(RS_BAR_RAW_FULL + slot));
+                        const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
+                        wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                        mbar_arrive_expect_tx(bar(C::BAR_RAW_FULL + slot), RS_RAW_CODES);
+                        tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.uq, g * 64, strip << 7, bar(C::BAR_RAW_FULL + slot));
                     }
                 }
                 for (int g = 0; g < ng; ++g, ++ri) {
-                    const uint32_t slot = ri % RS_RAW_DEPTH, ph = (ri / RS_RAW_DEPTH) & 1;
-                    wait_bounded(bar(RS_BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
-                    mbar_arrive_expect_tx(bar(RS_BAR_RAW_FULL + slot), RS_RAW_CODES + 128);
-                    tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.vq, g * 64, n0, bar(RS_BAR_RAW_FULL + slot));
+                    const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
+                    wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                    mbar_arrive_expect_tx(bar(C::BAR_RAW_FULL + slot), RS_RAW_CODES + 128);
+                    tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.vq, g * 64, n0, bar(C::BAR_RAW_FULL + slot));
                     bulk_g2s(rawr + slot * RS_RAW_SLOT + RS_RAW_CODES, p.vz + static_cast<size_t>(g) * p.N + n0, 128,
-                             bar(RS_BAR_RAW_FULL + slot));
+                             bar(C::BAR_RAW_FULL + slot));
                 }
             }
         }
@@ -387,10 +401,11 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             const uint32_t b = j & 1, jph = (j >> 1) & 1;
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);
             // us: rows m0.. of a (M, ng) array = 128 * ng consecutive bf16; vs: 128 consecutive bf16 per group
-            uint4 vu[2], vv[2];
+            constexpr int NV = C::GROUPS / 2;           // 16-byte vectors per lane: 16 * ng of each kind over 32 lanes
+            uint4 vu[NV], vv[NV];
             const long long u_first = static_cast<long long>(m0) * ng, u_total = static_cast<long long>(p.M) * ng;
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+            for (int t = 0; t < NV; ++t) {
                 const int vi = lane + 32 * t;             // 16-byte vector index, 16 * ng of each kind
                 vu[t] = make_uint4(0, 0, 0, 0);
                 vv[t] = make_uint4(0, 0, 0, 0);
@@ -407,9 +422,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     vv[t] = ldg16(p.vs + static_cast<size_t>(vi >> 4) * p.N + n0 + (vi & 15) * 8);
                 }
             }
-            wait_bounded(bar(RS_BAR_SC_EMPTY + b), jph ^ 1, abort_flag, p.status, 11);
+            wait_bounded(bar(C::BAR_SC_EMPTY + b), jph ^ 1, abort_flag, p.status, 11);
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+            for (int t = 0; t < NV; ++t) {
                 const int vi = lane + 32 * t;
                 if (vi < 16 * ng) {
                     const uint32_t wu[4] = {vu[t].x, vu[t].y, vu[t].z, vu[t].w};
@@ -427,7 +442,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(RS_BAR_SC_FULL + b));
+            if (lane == 0) mbar_arrive(bar(C::BAR_SC_FULL + b));
         }
     }
 

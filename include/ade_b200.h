@@ -159,7 +159,7 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
  *
  * the arithmetic of src/quantization.py:303-315 followed by the add of src/serving.py:92,
  * in the same order and with the same float32 roundings.  P_g is contracted with
- * tcgen05 kind::i8 MMAs into tensor memory.  Ranks up to 512 run a kernel that keeps a 128-row strip
+ * tcgen05 kind::i8 MMAs into tensor memory.  Ranks up to 1024 run a kernel that keeps a 128-row strip
  * of U expanded in shared memory and moves all global data with TMA (tensor maps are encoded per call
  * on the host; no device memory is allocated); larger ranks run the general kernel.
  *   w_b, w_out bf16 [M][N] (may not alias).  Requirements: N % 128 == 0, r % 128 == 0, M >= 1.

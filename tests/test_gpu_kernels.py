@@ -94,8 +94,11 @@ def test_recon_golden_bit_exact(path):
 
 
 @pytest.mark.parametrize("M,N,r", [(128, 128, 128), (256, 384, 256), (192, 128, 384), (100, 256, 512),
-                                   (384, 128, 1024), (1024, 1152, 640)])
+                                   (384, 128, 1024), (1024, 1152, 640), (2048, 2304, 768), (2100, 1920, 384),
+                                   (256, 256, 1152), (200, 384, 2048)])
 def test_recon_shapes_bit_exact(M, N, r):
+    """Ranks up to 512 and 640-1024 take the two configurations of the strip-resident kernel (several tiles and
+    strips per CTA in the larger cases), ranks above 1024 the general kernel."""
     case = _random_case(M, N, r, 1, seed=31 * M + N + r)
     out, acc = _run_recon(case)
     for g in range(r // 128):
