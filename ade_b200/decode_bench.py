@@ -1,6 +1,6 @@
 """Greedy decoding of a random-init LLaMA-architecture model with a synthetic delta on every linear module.
 
-    python -m ade_b200.decode_bench [--arch 7b|13b|tiny] [--layers L] [--batch B] [--prompt P] [--new N] [--seed S]
+    python -m ade_b200.decode_bench [--arch 7b|13b|tiny] [--layers L] [--batch B] [--prompt P] [--new N] [--seed S] [--no-fuse]
 
 Stands in for the whole-model configurations of the benchmark (no checkpoints or datasets are needed):
 the base model is random-init bfloat16 of the named architecture, every q/k/v/o/gate/up/down projection
@@ -8,7 +8,8 @@ carries a delta whose rank is drawn from a seed so that the total fits the alpha
 (`synth.draw_ranks`), packed fields are drawn directly (`random_packed` value ranges).  The prompt is run in
 one forward (factored path if batch * prompt <= 128 tokens, reconstructed path above), then N greedy steps
 on the factored path; the decode step is captured in a CUDA graph (static KV cache), and also timed
-eagerly.  Prints one JSON line.
+eagerly.  q/k/v and gate/up of every layer are served by one launch each (`fuse_kernel_linears`) unless
+--no-fuse is given.  Prints one JSON line.
 """
 from __future__ import annotations
 
@@ -19,7 +20,7 @@ import time
 import torch
 
 from . import synth
-from .serving import LINEAR_MODULE_NAMES, ADEKernelLinear
+from .serving import LINEAR_MODULE_NAMES, ADEKernelLinear, fuse_kernel_linears
 
 ARCH = {
     "7b": dict(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32),
@@ -38,7 +39,7 @@ def random_packed_cuda(d_o, d_i, rank, seed, device):
             "Vt_codes": r(rank, d_i).to(torch.uint8), "Vt_scale": s(ng, d_i), "Vt_zero": r(ng, d_i).to(torch.bfloat16)}
 
 
-def build_model(arch="7b", layers=None, seed=0, device="cuda", vocab=32000):
+def build_model(arch="7b", layers=None, seed=0, device="cuda", vocab=32000, fuse=True):
     from transformers import LlamaConfig, LlamaForCausalLM
 
     kw = dict(ARCH[arch])
@@ -64,14 +65,15 @@ def build_model(arch="7b", layers=None, seed=0, device="cuda", vocab=32000):
             packed = random_packed_cuda(d_o, d_i, ranks[i], 1000 * seed + i, device)
             setattr(parent, parts[1], ADEKernelLinear(lin.weight.data, packed))
             i += 1
-    return model, ranks
+    groups = fuse_kernel_linears(model) if fuse else 0
+    return model, ranks, groups
 
 
 @torch.no_grad()
-def run(arch="7b", layers=None, batch=1, prompt=64, new=128, seed=0, device="cuda"):
+def run(arch="7b", layers=None, batch=1, prompt=64, new=128, seed=0, device="cuda", fuse=True):
     from transformers import StaticCache
 
-    model, ranks = build_model(arch, layers, seed, device)
+    model, ranks, groups = build_model(arch, layers, seed, device, fuse=fuse)
     cfg = model.config
     g = torch.Generator().manual_seed(seed + 1)
     ids = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=g).to(device)
@@ -144,7 +146,7 @@ def run(arch="7b", layers=None, batch=1, prompt=64, new=128, seed=0, device="cud
         "batch": batch, "prompt": prompt, "new_tokens": new,
         "value": batch / t_graph, "unit": "tokens/s", "ms_per_step_graph": t_graph * 1e3,
         "eager_tokens_per_s": batch / t_eager, "prefill_s": t_prefill,
-        "rank_mean": sum(ranks) / n_mod, "graph_matches_eager_prefix": same, "data": "synthetic, random-init",
+        "rank_mean": sum(ranks) / n_mod, "fused_groups": groups, "graph_matches_eager_prefix": same, "data": "synthetic, random-init",
     }
 
 
@@ -156,8 +158,9 @@ def main():
     ap.add_argument("--prompt", type=int, default=64)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-fuse", action="store_true")
     a = ap.parse_args()
-    print(json.dumps(run(a.arch, a.layers, a.batch, a.prompt, a.new, a.seed)))
+    print(json.dumps(run(a.arch, a.layers, a.batch, a.prompt, a.new, a.seed, fuse=not a.no_fuse)))
 
 
 if __name__ == "__main__":

@@ -55,6 +55,7 @@ class ADEKernelLinear(nn.Module):
         for k in STORED_KEYS:
             self.register_buffer(f"p4_{k}", p4[k])
         self._p4 = None
+        self._group = None            # (FusedADEGroup, index) once fuse_kernel_linears has grouped this module
 
     def _stored_form(self) -> dict:
         """Stored form on the module's device (rebuilt after .to(device))."""
@@ -75,10 +76,113 @@ class ADEKernelLinear(nn.Module):
         if T == 0:
             return x2.new_empty(*shape[:-1], self.out_features)
         if T <= self.decode_max_tokens:
-            y = factored_forward(x2, self._stored_form(), weight=self.weight)
+            y = self._group[0].apply(self._group[1], x, x2) if self._group is not None else None
+            if y is None:
+                y = factored_forward(x2, self._stored_form(), weight=self.weight)
         else:
             y = F.linear(x2, self.merged_weight())
         return y.reshape(*shape[:-1], self.out_features)
+
+
+class FusedADEGroup:
+    """Several ADEKernelLinear modules that are always applied to the same input (q/k/v of an attention block,
+    gate/up of an MLP), served by ONE launch of the factored kernel per decode step.
+
+    The group is an ordinary ADE module in disguise: d_o = sum of the members' d_o, rank = sum of their ranks,
+    V^T = the members' V^T stacked along the rank axis, U = block diagonal.  Outside its own block a row of U
+    holds code 0 with zero-point 0 and scale 0, so the extra rank groups contribute exactly 0.0 and the kernel
+    needs no change; the price is the extra zero codes of U ((k - 1) * d_o * r / 2 bytes, ~1 % of the base weight)
+    against k - 1 launches, pipeline fills and grid-wide hand-overs saved.  The members' base weights become views
+    of one concatenated buffer (no copy is kept).  Only the factored path (T <= decode_max_tokens) is fused;
+    longer inputs go through the members' own reconstructed path.
+
+    This has no counterpart in the reference, which launches its kernels per module (src/serving.py:94-112).
+    """
+
+    def __init__(self, members):
+        self.members = list(members)
+        m0 = self.members[0]
+        dev = m0.weight.device
+        if any(m.in_features != m0.in_features or m.weight.device != dev or m.decode_max_tokens != m0.decode_max_tokens
+               for m in self.members):
+            raise ValueError("FusedADEGroup: members must share d_i, device and decode_max_tokens")
+        forms = [m._stored_form() for m in self.members]
+        Ms = [f["M"] for f in forms]
+        rs = [f["r"] for f in forms]
+        N, M, r = m0.in_features, sum(Ms), sum(rs)
+        ng = r // GROUP
+        self.offsets = [sum(Ms[:i]) for i in range(len(Ms) + 1)]
+        # base weights: one buffer, the members keep views of it
+        W = torch.cat([m.weight for m in self.members], dim=0)
+        for m, lo, hi in zip(self.members, self.offsets[:-1], self.offsets[1:]):
+            m._buffers["weight"] = W[lo:hi]
+        self.weight = W
+        uq = torch.zeros(M, r // 2, dtype=torch.uint8, device=dev)
+        us = torch.zeros(M, ng, dtype=forms[0]["us"].dtype, device=dev)
+        uz = torch.zeros(M, ng, dtype=torch.uint8, device=dev)
+        k0 = 0
+        for f, lo, hi in zip(forms, self.offsets[:-1], self.offsets[1:]):
+            uq[lo:hi, k0 // 2:(k0 + f["r"]) // 2] = f["uq"]
+            us[lo:hi, k0 // GROUP:(k0 + f["r"]) // GROUP] = f["us"]
+            uz[lo:hi, k0 // GROUP:(k0 + f["r"]) // GROUP] = f["uz"]
+            k0 += f["r"]
+        self.p4 = {
+            "uq": uq, "us": us, "uz": uz,
+            "vq": torch.cat([f["vq"] for f in forms], dim=1).contiguous(),
+            "vt": torch.cat([f["vt"] for f in forms], dim=0).contiguous(),
+            "vs": torch.cat([f["vs"] for f in forms], dim=0).contiguous(),
+            "vz": torch.cat([f["vz"] for f in forms], dim=0).contiguous(),
+            "M": M, "N": N, "r": r,
+        }
+        self._key = None
+        self._y = None
+        self._used = set()
+        for i, m in enumerate(self.members):
+            m._group = (self, i)
+
+    def apply(self, index: int, x, x2):
+        """Output of member `index` for the input x (x2 = x as a contiguous (T, d_i) bfloat16 matrix), or None when
+        the group cannot serve it (the members moved to another device since the group was built)."""
+        if self.members[0].weight.data_ptr() != self.weight.data_ptr():
+            return None
+        key = (x.data_ptr(), tuple(x.shape), x._version, x.dtype)
+        if self._y is None or key != self._key or index in self._used:
+            self._y = factored_forward(x2, self.p4, weight=self.weight)
+            self._key = key
+            self._used = set()
+        self._used.add(index)
+        y = self._y[:, self.offsets[index]:self.offsets[index + 1]]
+        if len(self._used) == len(self.members):
+            self._y = None                     # every member has taken its slice: nothing is served twice
+        return y
+
+
+# modules of a decoder layer that read the same activations
+FUSABLE_GROUPS = (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), ("mlp.gate_proj", "mlp.up_proj"))
+
+
+def fuse_kernel_linears(model, max_rank: int = 2048) -> int:
+    """Group q/k/v and gate/up of every decoder layer into FusedADEGroups (after the model is on its device).
+    A group is formed when all its modules are ADEKernelLinear and their ranks add up to at most `max_rank`
+    (the kernels' limit); q/k alone are tried when q/k/v does not fit.  Returns the number of groups."""
+    n = 0
+    for layer in _decoder_layers(model):
+        for names in FUSABLE_GROUPS:
+            mods = []
+            for sn in names:
+                try:
+                    m = layer.get_submodule(sn)
+                except AttributeError:
+                    m = None
+                mods.append(m)
+            if not all(isinstance(m, ADEKernelLinear) and m._group is None for m in mods):
+                continue
+            while len(mods) >= 2 and sum(m._dims[2] for m in mods) > max_rank:
+                mods = mods[:-1]
+            if len(mods) >= 2:
+                FusedADEGroup(mods)
+                n += 1
+    return n
 
 
 def _decoder_layers(model):

@@ -51,11 +51,12 @@ def test_config0_factored_q_proj():
     assert err0 > 2 * err
 
 
-@pytest.mark.parametrize("M,N,r,T", [(11008, 4096, 512, 1), (11008, 4096, 512, 8), (4096, 11008, 512, 8), (4096, 11008, 256, 16),
-                                     (11008, 4096, 1024, 3)])
+@pytest.mark.parametrize("M,N,r,T", [(11008, 4096, 512, 1), (11008, 4096, 512, 2), (11008, 4096, 512, 8), (4096, 11008, 512, 8),
+                                     (4096, 11008, 256, 16), (11008, 4096, 1024, 3)])
 def test_factored_mlp_modules_long_streams(M, N, r, T):
-    """Decode sizes on the MLP shapes of configs 2-4: every CTA streams more than 400 KB of W_b, which selects
-    the shared-memory FIFO variant of the factored kernel (d_i = 11008 also needs several staging waves)."""
+    """Decode sizes on the MLP shapes of configs 2-4: every CTA streams more than 400 KB of W_b, which for
+    2 <= T <= 16 selects the shared-memory FIFO variant of the factored kernel (d_i = 11008 also needs several
+    staging waves); T = 1 stays on the register-prefetch variant."""
     tp = synth.random_packed(M, N, r, 31 * T + r)
     W_b = synth.base_weight(M, N, 7)
     x = synth.activations(T, N, 8)

@@ -88,3 +88,81 @@ def test_model_forward_and_greedy_decode_match_merged_weights():
     assert (out[:, :12] == ids).all()
     # greedy tokens agree except where two logits are within rounding of each other
     assert (out == out_ref).float().mean().item() >= 0.8
+
+
+def test_fused_group_is_a_block_diagonal_module():
+    """q/k/v (or gate/up) as one ADE module: V^T stacked along the rank axis, U block diagonal with code 0,
+    zero-point 0 and scale 0 outside the blocks, base weights shared as views of one buffer."""
+    from ade_b200 import kernels
+    from ade_b200.serving import FusedADEGroup, fuse_kernel_linears
+
+    mods = []
+    for i, (M, r) in enumerate([(256, 128), (128, 256), (384, 128)]):
+        mods.append(ADEKernelLinear(synth.base_weight(M, 256, 20 + i), synth.random_packed(M, 256, r, 10 + i)))
+    singles = [{k: v.clone() if torch.is_tensor(v) else v for k, v in m._stored_form().items()} for m in mods]
+    weights = [m.weight.clone() for m in mods]
+    g = FusedADEGroup(mods)
+    assert (g.p4["M"], g.p4["N"], g.p4["r"]) == (768, 256, 512) and g.offsets == [0, 256, 384, 768]
+    U = kernels.unpack_nibbles(g.p4["uq"])
+    k0 = 0
+    for m, f, w, lo, hi in zip(mods, singles, weights, g.offsets[:-1], g.offsets[1:]):
+        r = f["r"]
+        assert torch.equal(U[lo:hi, k0:k0 + r], kernels.unpack_nibbles(f["uq"]))
+        assert int(U[lo:hi, :k0].sum()) == 0 and int(U[lo:hi, k0 + r:].sum()) == 0
+        assert torch.equal(g.p4["us"][lo:hi, k0 // 128:(k0 + r) // 128], f["us"])
+        assert float(g.p4["us"][lo:hi, :k0 // 128].float().abs().sum()) == 0.0
+        assert torch.equal(g.p4["vt"][k0:k0 + r], f["vt"]) and torch.equal(g.p4["vs"][k0 // 128:(k0 + r) // 128], f["vs"])
+        assert m.weight.data_ptr() == g.weight[lo:hi].data_ptr() and torch.equal(m.weight, w)
+        k0 += r
+    # model level: q/k/v and gate/up of every layer, unless the ranks do not fit
+    model = _tiny_model()
+    attach_kernel_linears(model, {k: v.clone() for k, v in model.state_dict().items()}, _deltas(model))
+    assert fuse_kernel_linears(model) == 4
+    assert model.model.layers[0].self_attn.o_proj._group is None
+    assert model.model.layers[1].mlp.up_proj._group[1] == 1
+    model2 = _tiny_model()
+    attach_kernel_linears(model2, {k: v.clone() for k, v in model2.state_dict().items()}, _deltas(model2))
+    assert fuse_kernel_linears(model2, max_rank=400) == 4          # q/k fit (256 + 128), v is left alone
+    assert model2.model.layers[0].self_attn.v_proj._group is None
+
+
+@pytest.mark.gpu
+def test_fused_groups_match_separate_launches():
+    """One launch for q/k/v and one for gate/up give what the per-module launches give (the base term bit for
+    bit per row; the delta term may be summed in another order over the warps)."""
+    from ade_b200.serving import FusedADEGroup, fuse_kernel_linears
+
+    dev = "cuda"
+    mods = []
+    for i, (M, r) in enumerate([(512, 256), (512, 128), (1024, 384)]):
+        mods.append(ADEKernelLinear(synth.base_weight(M, 768, 40 + i), synth.random_packed(M, 768, r, 50 + i)).to(dev))
+    for T in (1, 5, 16, 40):
+        x = synth.activations(T, 768, 60 + T).to(dev)
+        sep = [m(x) for m in mods]
+        g = FusedADEGroup(mods)
+        fused = [m(x) for m in mods]
+        assert g._y is None                                 # all three slices served from one launch
+        for a, b in zip(sep, fused):
+            err, cos = O.parity(b.float().cpu().numpy(), a.float().cpu().numpy())
+            assert err <= 2e-3 and cos >= 0.99999, (T, err, cos)
+        for m in mods:                                      # ungroup for the next round
+            m._group = None
+    # whole model: same greedy tokens with and without fusion, graph of calls unchanged
+    model = _tiny_model()
+    per_module = _deltas(model)
+    base_sd = {k: v.clone() for k, v in model.state_dict().items()}
+    attach_kernel_linears(model, base_sd, per_module)
+    model = model.to(dev)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 512, (2, 12), generator=g).to(dev)
+    with torch.no_grad():
+        plain = model(ids).logits.float().cpu().numpy()
+        out_plain = model.generate(ids, max_new_tokens=8, do_sample=False)
+        assert fuse_kernel_linears(model) == 4
+        fused = model(ids).logits.float().cpu().numpy()
+        out_fused = model.generate(ids, max_new_tokens=8, do_sample=False)
+        long_ids = torch.randint(0, 512, (1, 160), generator=g).to(dev)     # T > 128: the members' own reconstructed path
+        assert model(long_ids).logits.shape == (1, 160, 512)
+    err, cos = O.parity(fused, plain)
+    assert err <= 1e-2 and cos >= 0.9999, (err, cos)
+    assert (out_plain == out_fused).float().mean().item() >= 0.8
