@@ -337,6 +337,8 @@ __device__ __forceinline__ void xv_unit(const FactoredParams& p, float* redbuf, 
 // ---------------------------------------------------------------------------------------------
 // phase W: acc += W_b[rows] x^T over this warp's share of the d_i axis (blocks of 64 columns,
 // block b -> warp b % 8), weights and activations loaded DEPTH-1 blocks ahead.
+// Every CTA starts at another block (rotation by blockIdx.x): all CTAs read the same few kilobytes of x, and walking
+// them in step made every SM ask L2 for the same lines at the same time (measured: 4-6 % per call at T >= 4).
 // ---------------------------------------------------------------------------------------------
 template <int NT, int DEPTH, bool PREFETCH_X>
 __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
@@ -349,7 +351,8 @@ __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
         for (int hr = 0; hr < 2; ++hr) {
-            const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);     // rows past the slice: re-read the last one
+            // rows past the slice re-read the last one (L1 / L2 hits); predicating them off was measured slower
+            const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
             wrow[mt][hr] = p.w_b + static_cast<size_t>(m) * N + tig * 8;
         }
     const __nv_bfloat16* xrow[NT];
@@ -359,7 +362,7 @@ __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2
     uint4 A[DEPTH][2][2][2];
     uint4 X[PREFETCH_X ? DEPTH : 1][NT][2];
     auto load = [&](int d, int i) {
-        const int col = (warp + FA_WARPS * i) * 64;
+        const int col = (warp + FA_WARPS * ((i + static_cast<int>(blockIdx.x)) % cnt)) * 64;   // see wx_block's note on the rotation
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -374,7 +377,7 @@ __device__ __forceinline__ void wx_block(const FactoredParams& p, float (&acc)[2
         }
     };
     auto compute = [&](int d, int i) {
-        const int col = (warp + FA_WARPS * i) * 64;
+        const int col = (warp + FA_WARPS * ((i + static_cast<int>(blockIdx.x)) % cnt)) * 64;   // see wx_block's note on the rotation
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const bool live = nt * 8 + gid < T;
@@ -435,7 +438,7 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
     auto issue = [&](int q) {
         if (q < total) {
             const uint32_t sb = fs + (q % S) * ITEM;
-            const int col = (warp + FA_WARPS * qi) * 64 + tig * 8;
+            const int col = (warp + FA_WARPS * ((qi + static_cast<int>(blockIdx.x)) % cnt)) * 64 + tig * 8;   // rotated as in wx_block
             const int blk = row0 + qb * FA_ROWS;
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
