@@ -153,13 +153,11 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
     size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
     p.stages = 0;
     p.upf = 0;
-    // 2 to 16 tokens with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than registers
+    // Up to 16 tokens with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than registers
     // allow).  Short streams (a 4096 x 4096 module is 227 KB per CTA) are faster with the register prefetch: the
-    // deep FIFO raises the loaded memory latency, and the h hand-over pays it several times.  Measured on
-    // 11008 x 4096, r = 512: T = 8 29.9 -> 26.6 us, T = 2 29.3 -> 28.8 us, T = 1 29.5 -> 29.5 us (and slower at
-    // r = 1024), hence the token threshold.
+    // deep FIFO raises the loaded memory latency, and the h hand-over pays it several times.
     const size_t stream_bytes = static_cast<size_t>(p.M) * p.N * 2 / static_cast<size_t>(grid);
-    if (FUSE && ade::fa_side(NT) && stream_bytes >= kFifoMinStream && p.T >= 2) {
+    if (FUSE && ade::fa_side(NT) && stream_bytes >= kFifoMinStream) {
         const size_t room = (static_cast<size_t>(kMaxSmem) - smem) / ade::fa_fifo_item(NT);
         p.stages = room >= 2 ? static_cast<int>(room < static_cast<size_t>(ade::FA_FIFO_MAX) ? room : ade::FA_FIFO_MAX) : 0;
         smem += static_cast<size_t>(p.stages) * ade::fa_fifo_item(NT);

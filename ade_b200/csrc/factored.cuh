@@ -98,6 +98,9 @@ __device__ __forceinline__ void unpack8_bf16(uint32_t w, uint32_t (&e)[4]) {
 __device__ __forceinline__ void fa_cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
+__device__ __forceinline__ void fa_cp_async16_zfill(uint32_t dst_smem, const void* src, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(live ? 16 : 0) : "memory");
+}
 __device__ __forceinline__ void fa_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void fa_cp_async_wait(int n) {      // at most n of this thread's groups still in flight
     switch (n) {
@@ -451,8 +454,11 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
                 }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                fa_cp_async16(sb + (8 + 2 * nt) * STR, xrow[nt] + col - tig * 8);
-                fa_cp_async16(sb + (9 + 2 * nt) * STR, xrow[nt] + col - tig * 8 + 32);
+                // lanes whose token does not exist copy nothing (zero fill): eight lanes asking for the same
+                // 16 bytes of the last token made the stream measurably slower at T = 1 than at T = 8
+                const bool lv = nt * 8 + gid < T;
+                fa_cp_async16_zfill(sb + (8 + 2 * nt) * STR, xrow[nt] + col - tig * 8, lv);
+                fa_cp_async16_zfill(sb + (9 + 2 * nt) * STR, xrow[nt] + col - tig * 8 + 32, lv);
             }
             if (++qi == cnt) {
                 qi = 0;
