@@ -25,7 +25,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxRowsCap = 320;    // rows of one CTA's slice that fit the shared-memory y buffer (T = 128)
-constexpr size_t kFifoMinStream = 400 * 1024;   // bytes of W_b per CTA from which the FIFO pays off
+constexpr size_t kFifoMinStream = 400 * 1024;   // bytes of W_b per CTA from which the FIFO pays off at 9-16 tokens
 constexpr int kMaxSmem = 232448;     // opt-in dynamic shared memory per CTA on sm_100
 struct DeviceInfo {
     int ready = 0;      // 1 = usable, -1 = wrong architecture
@@ -153,11 +153,11 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
     size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
     p.stages = 0;
     p.upf = 0;
-    // Up to 16 tokens with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than registers
-    // allow).  Short streams (a 4096 x 4096 module is 227 KB per CTA) are faster with the register prefetch: the
-    // deep FIFO raises the loaded memory latency, and the h hand-over pays it several times.
+    // Up to 8 tokens, or up to 16 with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than
+    // registers allow).  At 9-16 tokens a short stream (a 4096 x 4096 module is 227 KB per CTA) is as fast with the
+    // register prefetch: the deep FIFO raises the loaded memory latency, which the h hand-over pays several times.
     const size_t stream_bytes = static_cast<size_t>(p.M) * p.N * 2 / static_cast<size_t>(grid);
-    if (FUSE && ade::fa_side(NT) && stream_bytes >= kFifoMinStream) {
+    if (FUSE && ade::fa_side(NT) && (NT == 1 || stream_bytes >= kFifoMinStream)) {
         const size_t room = (static_cast<size_t>(kMaxSmem) - smem) / ade::fa_fifo_item(NT);
         p.stages = room >= 2 ? static_cast<int>(room < static_cast<size_t>(ade::FA_FIFO_MAX) ? room : ade::FA_FIFO_MAX) : 0;
         smem += static_cast<size_t>(p.stages) * ade::fa_fifo_item(NT);
