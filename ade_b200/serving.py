@@ -5,7 +5,7 @@ decode_max_tokens, use_decode, use_recon, split_k)`` with ``forward(x)`` and the
 ``out_features / in_features / weight``, and ``build_kernel_model`` -- on top of the B200 kernels.
 Differences: tensors are bfloat16 (the reference module is float16), there is no float
 fallback (``use_decode`` / ``use_recon`` = False raise), and for T <= decode_max_tokens the base
-GEMM x W_b^T runs inside the factored kernel instead of a separate ``F.linear``.
+GEMM x W_b^T runs inside the factored kernel instead of a separate ``F.linear`` up to 32 tokens.
 """
 from __future__ import annotations
 
@@ -13,8 +13,14 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .kernels import (GROUP, STORED_KEYS, decode_kernel_status, factored_forward, pack_int4, recon_int4,
-                      recon_kernel_status)
+from .kernels import (GROUP, STORED_KEYS, decode_forward_packed, decode_kernel_status, factored_forward, pack_int4,
+                      recon_int4, recon_kernel_status)
+
+# Up to this many tokens the base GEMM x W_b^T runs inside the factored kernel (one launch, W_b streamed once by
+# a kernel built for skinny operands).  Above it cuBLAS is faster at the base term (measured on B200, 4096 x 4096:
+# T = 32 fused 22.7 us against 25.9 us split, T = 64 55.0 against 35.6), so the module falls back to the
+# reference's split: F.linear for the base, the kernel for the delta only.
+FUSED_BASE_MAX_TOKENS = 32
 
 # the seven linear modules of a LLaMA decoder layer (same list as src/adaptation.py:39-42)
 LINEAR_MODULE_NAMES = (
@@ -75,10 +81,13 @@ class ADEKernelLinear(nn.Module):
         T = x2.shape[0]
         if T == 0:
             return x2.new_empty(*shape[:-1], self.out_features)
-        if T <= self.decode_max_tokens:
+        if T <= FUSED_BASE_MAX_TOKENS and T <= self.decode_max_tokens:
             y = self._group[0].apply(self._group[1], x, x2) if self._group is not None else None
             if y is None:
                 y = factored_forward(x2, self._stored_form(), weight=self.weight)
+        elif T <= self.decode_max_tokens:
+            # the reference's own split (src/serving.py:106-111): library GEMM for the base term, kernel for the delta
+            y = decode_forward_packed(x2, F.linear(x2, self.weight), self._stored_form())
         else:
             y = F.linear(x2, self.merged_weight())
         return y.reshape(*shape[:-1], self.out_features)
