@@ -37,12 +37,16 @@ EXPORTS = (
 )
 
 
+MAX_BLOCKS = 4   # ADE_B200_MAX_BLOCKS
+
+
 class AdeDelta(ctypes.Structure):
     """struct ade_delta of include/ade_b200.h."""
     _fields_ = [
         ("uq", ctypes.c_void_p), ("vq", ctypes.c_void_p), ("vt", ctypes.c_void_p),
         ("us", ctypes.c_void_p), ("uz", ctypes.c_void_p), ("vs", ctypes.c_void_p), ("vz", ctypes.c_void_p),
         ("M", ctypes.c_int), ("N", ctypes.c_int), ("r", ctypes.c_int),
+        ("n_blocks", ctypes.c_int), ("block_rows", ctypes.c_int * (MAX_BLOCKS + 1)), ("block_groups", ctypes.c_int * (MAX_BLOCKS + 1)),
     ]
 
 

@@ -194,6 +194,23 @@ bool optin_factored() {
            cuda_ok(cudaFuncSetAttribute(ade::factored_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
 }
 
+// block-diagonal hint of the delta -> kernel parameters (validated: ascending, covering [0, M) x [0, ng))
+int set_blocks(ade::FactoredParams& p, const ade_delta_t* d) {
+    p.n_blocks = 0;
+    if (d->n_blocks == 0) return ADE_OK;
+    if (d->n_blocks < 0 || d->n_blocks > ADE_B200_MAX_BLOCKS) return ADE_ERR_SHAPE;
+    const int ng = d->r / ADE_B200_GROUP;
+    if (d->block_rows[0] != 0 || d->block_groups[0] != 0 || d->block_rows[d->n_blocks] != d->M || d->block_groups[d->n_blocks] != ng)
+        return ADE_ERR_SHAPE;
+    for (int i = 0; i <= d->n_blocks; ++i) {
+        if (i && (d->block_rows[i] <= d->block_rows[i - 1] || d->block_groups[i] <= d->block_groups[i - 1])) return ADE_ERR_SHAPE;
+        p.block_rows[i] = d->block_rows[i];
+        p.block_groups[i] = d->block_groups[i];
+    }
+    p.n_blocks = d->n_blocks;
+    return ADE_OK;
+}
+
 // ---- scratch of ade_b200_factored_static: lives in the library image, one copy per GPU that loads it.
 // Layout: 256 bytes holding the kernel's three sync words (always at the same place, whatever T and r),
 // then h = V^T x (bf16, T x r).  In host code this name is only a handle for cudaGetSymbolAddress.
@@ -275,6 +292,8 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     p.M = d->M;
     p.N = d->N;
     p.r = d->r;
+    rc = set_blocks(p, d);
+    if (rc) return rc;
     const int grid = di->sms;                                   // one persistent CTA per SM, all co-resident
     set_row_split(p, grid);
     if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;
@@ -330,6 +349,8 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     p.M = d->M;
     p.N = d->N;
     p.r = d->r;
+    rc = set_blocks(p, d);
+    if (rc) return rc;
     const int grid = di->sms;
     set_row_split(p, grid);
     if (p.rows_cap > kMaxRowsCap) return ADE_ERR_SHAPE;

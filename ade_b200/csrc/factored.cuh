@@ -65,7 +65,28 @@ struct FactoredParams {
     int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
     int stages;                    // depth of the shared-memory FIFO that streams W_b (0: register prefetch)
     int upf;                       // phase-U items per warp whose operands are prefetched into shared memory (0..FA_UPF)
+    int n_blocks;                  // block-diagonal U^: rows [block_rows[i], block_rows[i+1]) use groups
+    int block_rows[5];             // [block_groups[i], block_groups[i+1]) only; 0 blocks = dense
+    int block_groups[5];
 };
+
+// Rank groups that rows [blk, blk_end) can touch (union over the blocks they overlap).
+__device__ __forceinline__ void fa_group_range(const FactoredParams& p, int blk, int blk_end, int& g_lo, int& g_hi) {
+    g_lo = 0;
+    g_hi = p.r >> 7;
+    if (p.n_blocks > 0) {
+        int lo = g_hi, hi = 0;
+        for (int i = 0; i < p.n_blocks; ++i)
+            if (p.block_rows[i] < blk_end && p.block_rows[i + 1] > blk) {
+                lo = min(lo, p.block_groups[i]);
+                hi = max(hi, p.block_groups[i + 1]);
+            }
+        if (hi > lo) {
+            g_lo = lo;
+            g_hi = hi;
+        }
+    }
+}
 
 // Side warps stage the V codes, scales and zero-points of up to FA_STAGE_CHUNKS chunks of 128 columns per warp
 // (16 ranks x 64 bytes of codes, 256 bytes of scales, 128 bytes of zero-points per chunk) with cp.async, so that
@@ -526,13 +547,15 @@ __device__ __forceinline__ void fa_cp_async4(uint32_t dst_smem, const void* src)
 
 __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* ustage, int row0, int row1, int warp, int gid,
                                             int tig) {
-    const int ng = p.r >> 7, nitems = 2 * ng;
+    const int ng = p.r >> 7;
     const size_t rowb = static_cast<size_t>(p.r >> 1);
     const uint32_t us_s = smem_u32(ustage);
     int k = 0;
-    for (int blk = row0; blk < row1 && k < p.upf; blk += FA_ROWS)
-        for (int j = warp; j < nitems && k < p.upf; j += FA_WARPS, ++k) {
-            const int mt = j & 1, g = j >> 1;
+    for (int blk = row0; blk < row1 && k < p.upf; blk += FA_ROWS) {
+        int g_lo, g_hi;
+        fa_group_range(p, blk, min(blk + FA_ROWS, row1), g_lo, g_hi);
+        for (int j = warp; j < 2 * (g_hi - g_lo) && k < p.upf; j += FA_WARPS, ++k) {
+            const int mt = j & 1, g = g_lo + (j >> 1);
 #pragma unroll
             for (int hr = 0; hr < 2; ++hr) {
                 const int m = min(blk + mt * 16 + hr * 8 + gid, row1 - 1);
@@ -544,6 +567,7 @@ __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* us
                 fa_cp_async4(sc + 4, p.us + (e & ~static_cast<size_t>(1)));             // ... and the one that holds the scale
             }
         }
+    }
     fa_cp_async_commit();
 }
 
@@ -555,8 +579,10 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
     const int T = p.T, r = p.r;
     const int ng = r >> 7;
     const size_t rowb = static_cast<size_t>(r >> 1);
-    for (int j = warp; j < 2 * ng; j += FA_WARPS, ++k) {
-        const int mt = j & 1, g = j >> 1;
+    int g_lo, g_hi;
+    fa_group_range(p, blk, min(blk + FA_ROWS, row_end), g_lo, g_hi);
+    for (int j = warp; j < 2 * (g_hi - g_lo); j += FA_WARPS, ++k) {
+        const int mt = j & 1, g = g_lo + (j >> 1);
         uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
         float su[2];
 #pragma unroll

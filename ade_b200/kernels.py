@@ -124,6 +124,13 @@ def _cdelta(p4: dict):
             if not (t.is_cuda and t.is_contiguous()):
                 raise ValueError(f"stored form tensor {k} must be a contiguous CUDA tensor")
         d = _lib.AdeDelta(*key, int(p4["M"]), int(p4["N"]), int(p4["r"]))
+        blocks = p4.get("blocks")              # [(row_begin, group_begin), ..., (M, ng)] of a block-diagonal U^
+        if blocks:
+            if not 2 <= len(blocks) <= _lib.MAX_BLOCKS + 1:
+                raise ValueError("stored form: at most %d blocks" % _lib.MAX_BLOCKS)
+            d.n_blocks = len(blocks) - 1
+            for i, (row, grp) in enumerate(blocks):
+                d.block_rows[i], d.block_groups[i] = int(row), int(grp)
         c = p4["_cdelta"] = (key, d)
     return c[1]
 

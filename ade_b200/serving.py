@@ -142,6 +142,8 @@ class FusedADEGroup:
             "vs": torch.cat([f["vs"] for f in forms], dim=0).contiguous(),
             "vz": torch.cat([f["vz"] for f in forms], dim=0).contiguous(),
             "M": M, "N": N, "r": r,
+            # rows of member i use only its own rank groups: the kernel skips the zero blocks of U
+            "blocks": [(self.offsets[i], sum(rs[:i]) // GROUP) for i in range(len(Ms) + 1)] if len(Ms) <= 4 else None,
         }
         self._key = None
         self._y = None

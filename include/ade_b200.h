@@ -25,6 +25,7 @@ extern "C" {
 
 #define ADE_B200_GROUP 128          /* ranks per quantization group (G); the only supported value */
 #define ADE_B200_MAX_RANK 2048
+#define ADE_B200_MAX_BLOCKS 4          /* blocks of a block-diagonal U^ (ade_delta_t.n_blocks) */
 #define ADE_B200_MAX_TOKENS 128     /* largest T of the factored path (src/serving.py:105) */
 
 /* return codes */
@@ -80,6 +81,14 @@ typedef struct ade_delta {
     const uint16_t* vs;
     const uint8_t* vz;
     int M, N, r;
+    /* Optional hint for a block-diagonal U^ (several modules that share their input served as one, see
+     * INTEGRATION.md section 6): rows [block_rows[i], block_rows[i+1]) hold non-zero codes only in the rank
+     * groups [block_groups[i], block_groups[i+1]), i < n_blocks <= ADE_B200_MAX_BLOCKS, and (code - zero) is
+     * exactly 0 elsewhere.  The factored kernel then skips the other groups of those rows.  n_blocks = 0: dense.
+     * No counterpart in the reference. */
+    int n_blocks;
+    int block_rows[ADE_B200_MAX_BLOCKS + 1];
+    int block_groups[ADE_B200_MAX_BLOCKS + 1];
 } ade_delta_t;
 
 /* Library / device checks.  Replaces decode_kernel_status / recon_kernel_status

@@ -147,6 +147,27 @@ def test_fused_groups_match_separate_launches():
             assert err <= 2e-3 and cos >= 0.99999, (T, err, cos)
         for m in mods:                                      # ungroup for the next round
             m._group = None
+    # the block hint is validated before any launch: it must tile [0, M) x [0, ng) in ascending order
+    import ctypes
+    from ade_b200 import _lib, kernels
+    g = FusedADEGroup(mods)
+    d = kernels._cdelta(g.p4)
+    assert d.n_blocks == 3 and list(d.block_rows)[:4] == [0, 512, 1024, 2048] and list(d.block_groups)[:4] == [0, 2, 3, 6]
+    x = synth.activations(4, 768, 61).to(dev)
+    out = torch.empty(4, 2048, dtype=torch.bfloat16, device=dev)
+    scratch = torch.zeros(1 << 20, dtype=torch.uint8, device=dev)
+    lib = _lib.load()
+    call = lambda: lib.ade_b200_factored(ctypes.byref(d), x.data_ptr(), None, g.weight.data_ptr(), out.data_ptr(),
+                                         scratch.data_ptr(), scratch.numel(), 4, None)
+    assert call() == 0
+    d.block_rows[1] = 1024                              # not ascending
+    assert call() == -2
+    d.block_rows[1] = 512
+    d.block_groups[3] = 5                               # does not end at ng
+    assert call() == -2
+    g.p4.pop("_cdelta")
+    for m in mods:
+        m._group = None
     # whole model: same greedy tokens with and without fusion, graph of calls unchanged
     model = _tiny_model()
     per_module = _deltas(model)
