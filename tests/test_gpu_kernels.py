@@ -95,7 +95,7 @@ def test_recon_golden_bit_exact(path):
 
 @pytest.mark.parametrize("M,N,r", [(128, 128, 128), (256, 384, 256), (192, 128, 384), (100, 256, 512),
                                    (384, 128, 1024), (1024, 1152, 640), (2048, 2304, 768), (2100, 1920, 384),
-                                   (256, 256, 1152), (200, 384, 2048)])
+                                   (256, 256, 1152), (200, 384, 2048), (1, 128, 128), (129, 128, 256)])
 def test_recon_shapes_bit_exact(M, N, r):
     """Ranks up to 512 and 640-1024 take the two configurations of the strip-resident kernel (several tiles and
     strips per CTA in the larger cases), ranks above 1024 the general kernel."""
@@ -144,8 +144,10 @@ def test_factored_token_counts(T):
     _check_factored(case, False)
 
 
-@pytest.mark.parametrize("M,N,r", [(32, 128, 128), (160, 256, 384), (512, 1152, 1024), (1024, 2048, 1152)])
+@pytest.mark.parametrize("M,N,r", [(32, 128, 128), (160, 256, 384), (512, 1152, 1024), (1024, 2048, 1152), (1, 128, 128),
+                                   (7, 256, 2048), (333, 384, 256)])
 def test_factored_shapes(M, N, r):
+    """Ragged row counts (fewer rows than CTAs, a single row), the smallest d_i and the largest rank."""
     _check_factored(_random_case(M, N, r, 5, seed=M + N + r), True)
     _check_factored(_random_case(M, N, r, 19, seed=M + N + r + 1), True)
 
