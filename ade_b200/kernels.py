@@ -10,6 +10,7 @@ raises.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -136,6 +137,14 @@ def _cdelta(p4: dict):
 
 
 # ---------------------------------------------------------------------------- launches
+_NULL = contextlib.nullcontext()
+
+
+def _on_device(dev: torch.device):
+    """Device guard for a launch; free when `dev` is already current (the guard costs ~10 us of host time)."""
+    return _NULL if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+
 _scratch: dict = {}
 
 
@@ -187,7 +196,7 @@ def factored_forward(x: torch.Tensor, p4: dict, weight: torch.Tensor | None = No
         if y_dense.shape[0] != T:
             raise ValueError("y_dense and x disagree on T")
     out = torch.empty((T, M), dtype=torch.bfloat16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
         nbytes = lib.ade_b200_factored_scratch_bytes(T, r)
         scratch = _scratch_for(x.device, stream, T, r, nbytes)
@@ -229,7 +238,7 @@ def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None):
     if dbg_acc is not None and not (dbg_acc.dtype == torch.int32 and dbg_acc.is_contiguous()
                                     and tuple(dbg_acc.shape) == (r // GROUP, M, N)):
         raise ValueError("dbg_acc must be a contiguous int32 (ng, d_o, d_i) tensor")
-    with torch.cuda.device(base.device):
+    with _on_device(base.device):
         rc = lib.ade_b200_recon(
             ctypes.byref(_cdelta(p4)), base.data_ptr(), out.data_ptr(),
             None if dbg_acc is None else dbg_acc.data_ptr(),
