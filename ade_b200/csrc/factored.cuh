@@ -21,7 +21,8 @@
 // are the 16-row operand of a warp MMA; the activations (x or h, L1/L2 resident) are the 8-column operand.
 // Two variants of the W_b stream: 128-bit loads into registers two or three blocks ahead of their use, or
 // (FIFO = true: up to 8 tokens, and up to 16 for long streams) per-thread cp.async copies into a FIFO in
-// shared memory up to five blocks ahead, with the side warps staging their operands a wave at a time.
+// shared memory (as many stages as fit, three at present), with the side warps staging their operands a wave at
+// a time.
 // The contraction axis is split over the 8 warps of a CTA and reduced through shared memory in a
 // fixed order, so results do not depend on scheduling (no floating-point atomics).
 //
