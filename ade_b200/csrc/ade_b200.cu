@@ -143,7 +143,8 @@ __global__ void pack_zeros_kernel(const uint16_t* __restrict__ z, uint8_t* __res
 void set_row_split(ade::FactoredParams& p, int grid) {
     const int n_units = p.r / 16;
     const int unit_ctas = n_units < grid ? n_units : grid;
-    p.unit_rows = (p.w_b != nullptr && p.M / grid >= 24 && p.T > 16) ? 14 : 0;   // side warps hide the unit at T <= 16
+    // side warps hide the unit at T <= 16; with sliced units (parts > 1) nearly every CTA owns one
+    p.unit_rows = (p.w_b != nullptr && p.M / grid >= 24 && p.T > 16 && p.parts == 1) ? 14 : 0;
     const long long budget = static_cast<long long>(p.M) + static_cast<long long>(unit_ctas) * p.unit_rows;
     p.rows_cap = static_cast<int>(((budget + grid - 1) / grid + 1 + 31) / 32 * 32);
 }
@@ -161,6 +162,14 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
         const size_t room = (static_cast<size_t>(kMaxSmem) - smem) / ade::fa_fifo_item(NT);
         p.stages = room >= 2 ? static_cast<int>(room < static_cast<size_t>(ade::FA_FIFO_MAX) ? room : ade::FA_FIFO_MAX) : 0;
         smem += static_cast<size_t>(p.stages) * ade::fa_fifo_item(NT);
+    }
+    p.hstage = 0;
+    if (!ade::fa_side(NT)) {                             // T > 16: h is staged in shared memory when it fits
+        const size_t hs_bytes = ade::fa_side_region(p.T, p.r);
+        if (smem + hs_bytes <= static_cast<size_t>(kMaxSmem)) {
+            p.hstage = 1;
+            smem += hs_bytes;
+        }
     }
     // operands of the first phase-U items are prefetched into shared memory: the drained FIFO, or an area of their own
     if (p.stages >= 2) {
@@ -249,16 +258,38 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
     return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
 
+// h: bf16 [T][r]; for T <= 16 two float32 partial sums [2][T][r] (each half of d_i is summed by another CTA);
+// then the sync words.  This much is required.
+static size_t factored_scratch_min(int T, int r) {
+    const size_t b = static_cast<size_t>(T) * r * (T <= 16 ? 2 * sizeof(float) : sizeof(__nv_bfloat16));
+    return ((b + 255) & ~static_cast<size_t>(255)) + 256;
+}
+// T > 16: slices of d_i per 16-rank unit of phase A, so that about 128 CTAs share it instead of r / 16
+static int factored_parts_wanted(int T, int r) { return T <= 16 || r >= 2048 ? 1 : (2048 / r > 8 ? 8 : 2048 / r); }
+
 size_t ade_b200_factored_scratch_bytes(int T, int r) {
     if (T < 1 || r < 1) return 0;
-    // h: bf16 [T][r]; for T <= 16 two float32 partial sums [2][T][r] (each half of d_i is summed by another CTA)
-    const size_t b = static_cast<size_t>(T) * r * (T <= 16 ? 2 * sizeof(float) : sizeof(__nv_bfloat16));
-    return ((b + 255) & ~static_cast<size_t>(255)) + 256;          // h, then the three sync words
+    const int parts = factored_parts_wanted(T, r);
+    // recommended size: behind the sync words, float32 [parts][T][r] partial sums (T > 16)
+    return factored_scratch_min(T, r) + (parts > 1 ? static_cast<size_t>(parts) * T * r * sizeof(float) : 0);
 }
 
 size_t ade_b200_factored_sync_offset(int T, int r) {
-    const size_t n = ade_b200_factored_scratch_bytes(T, r);
-    return n ? n - 256 : 0;
+    if (T < 1 || r < 1) return 0;
+    return factored_scratch_min(T, r) - 256;
+}
+
+// how many slices fit behind the sync words of a scratch buffer of `bytes` bytes (1 = unsplit units)
+static int factored_parts(int T, int r, int N, size_t bytes, bool fused_base) {
+    // With the base GEMM in the same launch the units stay whole: slicing would put phase A in front of every CTA's
+    // stream of W_b instead of r / 16 of them (measured slower on 11008 x 4096 at T = 24-32).
+    int parts = fused_base ? 1 : factored_parts_wanted(T, r);
+    const int by_chunks = (N >> 7) / 8;                       // at least one 128-column chunk per warp and slice
+    if (parts > by_chunks) parts = by_chunks;
+    const size_t room = bytes - factored_scratch_min(T, r);
+    const size_t per = static_cast<size_t>(T) * r * sizeof(float);
+    if (static_cast<size_t>(parts) * per > room) parts = static_cast<int>(room / per);
+    return parts < 2 ? 1 : parts;
 }
 
 int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b, void* out,
@@ -271,7 +302,7 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     if (!aligned16(d->vt) || !aligned16(x) || !aligned16(out) || !aligned16(scratch) ||
         (y_dense && !aligned16(y_dense)) || (w_b && !aligned16(w_b)))
         return ADE_ERR_ALIGN;
-    if (scratch_bytes < ade_b200_factored_scratch_bytes(T, d->r)) return ADE_ERR_SCRATCH;
+    if (scratch_bytes < factored_scratch_min(T, d->r)) return ADE_ERR_SCRATCH;
     const DeviceInfo* di = nullptr;
     rc = device_info(&di);
     if (rc) return rc;
@@ -287,6 +318,8 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     p.vz = d->vz;
     p.h = static_cast<__nv_bfloat16*>(scratch);
     p.sync = reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + ade_b200_factored_sync_offset(T, d->r));
+    p.parts = factored_parts(T, d->r, d->N, scratch_bytes, w_b != nullptr);
+    p.hpart = reinterpret_cast<float*>(static_cast<char*>(scratch) + factored_scratch_min(T, d->r));
     p.out = static_cast<__nv_bfloat16*>(out);
     p.T = T;
     p.M = d->M;
@@ -344,6 +377,13 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     p.vz = d->vz;
     p.sync = reinterpret_cast<unsigned int*>(base);
     p.h = reinterpret_cast<__nv_bfloat16*>(base + 256);
+    {
+        // what is left of the array behind h takes the partial sums of sliced phase-A units (T > 16)
+        const size_t h_end = 256 + ((h_bytes + 255) & ~static_cast<size_t>(255));
+        const size_t room = ADE_B200_STATIC_SCRATCH_BYTES > h_end ? ADE_B200_STATIC_SCRATCH_BYTES - h_end : 0;
+        p.parts = factored_parts(T, d->r, d->N, factored_scratch_min(T, d->r) + room, w_b != nullptr);
+        p.hpart = reinterpret_cast<float*>(base + h_end);
+    }
     p.out = static_cast<__nv_bfloat16*>(out);
     p.T = T;
     p.M = d->M;

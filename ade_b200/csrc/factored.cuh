@@ -59,13 +59,16 @@ struct FactoredParams {
     const uint16_t* vs;            // [ng][N]
     const uint8_t* vz;             // [ng][N]
     __nv_bfloat16* h;              // scratch: bf16 [T][r], or float32 [2][T][r] partial sums when T <= 16
-    unsigned int* sync;            // scratch: [0] units arrived, [1] CTAs done, [2] status (0 = ok)
+    float* hpart;                  // scratch, T > 16 and parts > 1: float32 [parts][T][r] partial sums of h
+    int parts;                     // T > 16: every 16-rank unit of phase A is split over this many slices of d_i
+    unsigned int* sync;            // scratch: [0] units arrived, [1] CTAs done, [2] status (0 = ok), [3] slices of h reduced
     __nv_bfloat16* out;            // [T][M]
     int T, M, N, r;
     int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
     int unit_rows;                 // rows a CTA gives up for the phase-A unit it owns
     int stages;                    // depth of the shared-memory FIFO that streams W_b (0: register prefetch)
     int upf;                       // phase-U items per warp whose operands are prefetched into shared memory (0..FA_UPF)
+    int hstage;                    // T > 16: h (bf16 [T][r]) is copied to shared memory before phase U (when it fits)
     int n_blocks;                  // block-diagonal U^: rows [block_rows[i], block_rows[i+1]) use groups
     int block_rows[5];             // [block_groups[i], block_groups[i+1]) only; 0 blocks = dense
     int block_groups[5];
@@ -541,13 +544,16 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
 // grid-wide wait for h (they do not depend on it), which takes their memory round trip off the path behind it.
 // ---------------------------------------------------------------------------------------------
 constexpr int FA_UPF = 4;
+// phase-U work items per (m16 tile, rank group): the token tiles are shared out as well when there are many, so that
+// all eight warps have work at small ranks
+__host__ __device__ constexpr int fa_u_split(int NT) { return NT >= 16 ? 4 : (NT >= 8 ? 2 : 1); }
 constexpr int FA_UPF_ITEM = FA_THREADS * (2 * 16 + 2 * 8);     // per item and thread: two 16-byte code pieces, two (zero, scale) word pairs
 __device__ __forceinline__ void fa_cp_async4(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 
 __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* ustage, int row0, int row1, int warp, int gid,
-                                            int tig) {
+                                            int tig, int ns) {
     const int ng = p.r >> 7;
     const size_t rowb = static_cast<size_t>(p.r >> 1);
     const uint32_t us_s = smem_u32(ustage);
@@ -555,8 +561,8 @@ __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* us
     for (int blk = row0; blk < row1 && k < p.upf; blk += FA_ROWS) {
         int g_lo, g_hi;
         fa_group_range(p, blk, min(blk + FA_ROWS, row1), g_lo, g_hi);
-        for (int j = warp; j < 2 * (g_hi - g_lo) && k < p.upf; j += FA_WARPS, ++k) {
-            const int mt = j & 1, g = g_lo + (j >> 1);
+        for (int j = warp; j < 2 * (g_hi - g_lo) * ns && k < p.upf; j += FA_WARPS, ++k) {
+            const int jj = j / ns, mt = jj & 1, g = g_lo + (jj >> 1);
 #pragma unroll
             for (int hr = 0; hr < 2; ++hr) {
                 const int m = min(blk + mt * 16 + hr * 8 + gid, row1 - 1);
@@ -582,8 +588,10 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
     const size_t rowb = static_cast<size_t>(r >> 1);
     int g_lo, g_hi;
     fa_group_range(p, blk, min(blk + FA_ROWS, row_end), g_lo, g_hi);
-    for (int j = warp; j < 2 * (g_hi - g_lo); j += FA_WARPS, ++k) {
-        const int mt = j & 1, g = g_lo + (j >> 1);
+    constexpr int NS = fa_u_split(NT);
+    for (int j = warp; j < 2 * (g_hi - g_lo) * NS; j += FA_WARPS, ++k) {
+        const int part = j % NS, jj = j / NS;               // token tiles [part * NT / NS, (part + 1) * NT / NS)
+        const int mt = jj & 1, g = g_lo + (jj >> 1);
         uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
         float su[2];
 #pragma unroll
@@ -617,13 +625,14 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
         const int kb = g * 128 + tig * 32;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
+            if (NS > 1 && nt / (NT / NS) != part) continue;
             const int tok = nt * 8 + gid;
             float pa[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 uint4 hq = make_uint4(0u, 0u, 0u, 0u);
                 if (tok < T) {
-                    if (SPLIT) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
+                    if (SPLIT || hs != nullptr) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
                     else hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
                 }
                 mma_bf16(pa, a[0][4 * wi], a[1][4 * wi], a[0][4 * wi + 1], a[1][4 * wi + 1], hq.x, hq.y);
@@ -670,7 +679,8 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     float* ybuf = side_red + (SIDE ? FA_SIDE_WARPS * 32 * 17 : 0);     // [rows_cap][YS]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int G = gridDim.x, c = blockIdx.x;
-    const int n_units = (p.r >> 4) * (SIDE ? 2 : 1);       // with side warps a unit is 16 ranks x half of d_i
+    const int parts = SIDE ? 2 : p.parts;                  // slices of d_i per 16 ranks (side warps: two halves)
+    const int n_units = (p.r >> 4) * parts;
     const int unit_ctas = min(n_units, G);
     const int nchunks = p.N >> 7;
     const int row0 = slice_start(c, G, p.M, unit_ctas, p.unit_rows);
@@ -697,7 +707,9 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     if (!SIDE) {
         unsigned int done = 0;
         for (int u = G - 1 - c; u < n_units; u += G) {
-            xv_unit<NT, FA_WARPS>(p, fsmem, u * 16, 0, nchunks, nullptr, warp, gid, tig);
+            const int part = u % parts, kb = u / parts;
+            xv_unit<NT, FA_WARPS>(p, fsmem, kb * 16, part * nchunks / parts, (part + 1) * nchunks / parts,
+                                  parts > 1 ? p.hpart + static_cast<size_t>(part) * p.T * p.r : nullptr, warp, gid, tig);
             ++done;
         }
         if (done && threadIdx.x == 0) {                    // xv_unit ended with a barrier of the main warps
@@ -720,11 +732,21 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         }
     }
 
+    if (!FUSE_WB) {
+        // Base term supplied by the caller: this CTA's rows of y_dense go to the y buffer now, while h is still being
+        // computed elsewhere, so that the store loop of phase U does not wait for a global load per element.
+        const int rows = row1 - row0;
+        for (int e = threadIdx.x; e < rows * p.T; e += FA_THREADS) {
+            const int t = e / rows, rr = e - t * rows;
+            ybuf[static_cast<size_t>(rr) * YS + t] = __bfloat162float(p.y_dense[static_cast<size_t>(t) * p.M + row0 + rr]);
+        }
+    }
     // operands of the first phase-U items: in flight while this CTA waits for h.  The stream variant reuses its
     // FIFO (drained by now), the others have an area of their own behind the h tile.
     uint8_t* ustage = FIFO ? const_cast<uint8_t*>(fifo)
-                           : reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * YS) + (SIDE ? fa_side_region(p.T, p.r) : 0);
-    if (p.upf > 0) uh_prefetch(p, ustage, row0, row1, warp, gid, tig);
+                           : reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * YS) +
+                                 (SIDE || p.hstage ? fa_side_region(p.T, p.r) : 0);
+    if (p.upf > 0) uh_prefetch(p, ustage, row0, row1, warp, gid, tig, fa_u_split(NT));
 
     // ---- wait for every h unit (bounded; on expiry record a status and carry on)
     if (threadIdx.x == 0) {
@@ -737,7 +759,60 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         }
     }
     main_sync();
+    if (!SIDE && parts > 1) {
+        // The slices of d_i were summed by different CTAs: every CTA now adds the partial sums of its share of
+        // the T x r elements, rounds to bf16 once and publishes them; phase U starts when all shares are there.
+        const int quads = (p.T * p.r) >> 2;
+        const int q0 = static_cast<int>(static_cast<long long>(c) * quads / G);
+        const int q1 = static_cast<int>(static_cast<long long>(c + 1) * quads / G);
+        const size_t stride = static_cast<size_t>(p.T) * p.r;
+        for (int i = q0 + threadIdx.x; i < q1; i += FA_THREADS) {
+            uint4 a = ldcg16(p.hpart + 4 * static_cast<size_t>(i));
+            float s0 = __uint_as_float(a.x), s1 = __uint_as_float(a.y), s2 = __uint_as_float(a.z), s3 = __uint_as_float(a.w);
+            for (int k = 1; k < parts; ++k) {
+                a = ldcg16(p.hpart + k * stride + 4 * static_cast<size_t>(i));
+                s0 += __uint_as_float(a.x);
+                s1 += __uint_as_float(a.y);
+                s2 += __uint_as_float(a.z);
+                s3 += __uint_as_float(a.w);
+            }
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(s0, s1), hi = __floats2bfloat162_rn(s2, s3);
+            uint2 v;
+            v.x = *reinterpret_cast<const uint32_t*>(&lo);
+            v.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(p.h + 4 * static_cast<size_t>(i)) = v;
+        }
+        main_sync();
+        if (threadIdx.x == 0) {
+            red_release_gpu_add(p.sync + 3, 1u);
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(p.sync + 3) < static_cast<unsigned int>(G)) {
+                if (clock64() - t0 > FA_SPIN_LIMIT) {
+                    atomicExch(p.sync + 2, 1u);
+                    break;
+                }
+            }
+        }
+        main_sync();
+    }
     __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(ybuf + static_cast<size_t>(p.rows_cap) * YS);   // [T][r + 8]
+    if (!SIDE) {
+        if (p.hstage) {
+            // h into shared memory in one sweep of 16-byte copies: phase U would otherwise fetch it from L2 in small
+            // dependent loads, 64 per work item at T = 128
+            const int per_row = p.r >> 3, pieces = p.T * per_row;
+            const uint32_t hs_s = smem_u32(hs);
+            for (int i = threadIdx.x; i < pieces; i += FA_THREADS) {
+                const int t = i / per_row, k8 = i - t * per_row;
+                fa_cp_async16(hs_s + (static_cast<uint32_t>(t) * (p.r + 8) + 8 * k8) * 2, p.h + static_cast<size_t>(t) * p.r + 8 * k8);
+            }
+            fa_cp_async_commit();
+            fa_cp_async_wait(0);
+            main_sync();
+        } else {
+            hs = nullptr;
+        }
+    }
     if (SIDE) {
         // the two float32 halves of h, summed, rounded to bf16 once and kept in shared memory for phase U
         const float* h0 = reinterpret_cast<const float*>(p.h);
@@ -767,13 +842,12 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         uh_block<NT, SIDE>(p, acc, blk, row1, hs, ustage, uk, warp, gid, tig);
         const float* yb = ybuf + static_cast<size_t>(blk - row0) * YS;
         const int T = p.T, M = p.M;
-        const __nv_bfloat16* yd = p.y_dense;
         __nv_bfloat16* out = p.out;
         reduce_tiles<NT>(red, acc, warp, gid, tig, [=](int row, int t, float s) {
             const int m = blk + row;
             if (m < row1 && t < T) {
                 const size_t o = static_cast<size_t>(t) * M + m;
-                s += FUSE_WB ? yb[row * YS + t] : __bfloat162float(yd[o]);
+                s += yb[row * YS + t];
                 out[o] = __float2bfloat16_rn(s);
             }
         });
@@ -786,6 +860,7 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {
             atomicExch(p.sync, 0u);
             atomicExch(p.sync + 1, 0u);
+            atomicExch(p.sync + 3, 0u);
         }
     }
 }

@@ -5,7 +5,7 @@ decode_max_tokens, use_decode, use_recon, split_k)`` with ``forward(x)`` and the
 ``out_features / in_features / weight``, and ``build_kernel_model`` -- on top of the B200 kernels.
 Differences: tensors are bfloat16 (the reference module is float16), there is no float
 fallback (``use_decode`` / ``use_recon`` = False raise), and for T <= decode_max_tokens the base
-GEMM x W_b^T runs inside the factored kernel instead of a separate ``F.linear`` up to 32 tokens.
+GEMM x W_b^T runs inside the factored kernel instead of a separate ``F.linear`` up to 16 tokens.
 """
 from __future__ import annotations
 
@@ -17,10 +17,11 @@ from .kernels import (GROUP, STORED_KEYS, decode_forward_packed, decode_kernel_s
                       recon_int4, recon_kernel_status)
 
 # Up to this many tokens the base GEMM x W_b^T runs inside the factored kernel (one launch, W_b streamed once by
-# a kernel built for skinny operands).  Above it cuBLAS is faster at the base term (measured on B200, 4096 x 4096:
-# T = 32 fused 22.7 us against 25.9 us split, T = 64 55.0 against 35.6), so the module falls back to the
-# reference's split: F.linear for the base, the kernel for the delta only.
-FUSED_BASE_MAX_TOKENS = 32
+# a kernel built for skinny operands, h computed by side warps under the stream).  Above it cuBLAS is faster at the
+# base term, so the module falls back to the reference's split: F.linear for the base, the kernel for the delta
+# only (measured on B200 per call, fused / split: 4096 x 4096 T = 16 14.5 / 21.0 us, T = 32 22.4 / 23.7, T = 64
+# 46.3 / 29.2; 11008 x 4096 T = 16 30.1 / 34.0, T = 24 40.6 / 39.2, T = 64 117.6 / 55.9).
+FUSED_BASE_MAX_TOKENS = 16
 
 # the seven linear modules of a LLaMA decoder layer (same list as src/adaptation.py:39-42)
 LINEAR_MODULE_NAMES = (

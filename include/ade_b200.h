@@ -119,14 +119,18 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
  * src/kernels.py:1182-1200), or sum_n w_b[m][n] x[t][n] computed inside the same kernel
  * when w_b != NULL (exactly one of the two must be given).
  *   x bf16 [T][N], y_dense bf16 [T][M], w_b bf16 [M][N], out bf16 [T][M].
- *   scratch: device buffer of at least ade_b200_factored_scratch_bytes(T, r) bytes.  It holds
+ *   scratch: device buffer, ade_b200_factored_scratch_bytes(T, r) bytes recommended.  It holds
  *   h = V^T x (bf16 [T][r]; for T <= 16 two float32 partial sums [2][T][r], one per half of the
- *   d_i axis) and, at byte offset ade_b200_factored_sync_offset(T, r), three
- *   32-bit words used to order the phases of the kernel: they must be ZERO before the first
+ *   d_i axis), at byte offset ade_b200_factored_sync_offset(T, r) 256 bytes of which the first four
+ *   32-bit words order the phases of the kernel, and behind them, for T > 16, float32 partial sums
+ *   [parts][T][r] that let about 128 CTAs share the computation of h instead of r / 16 (parts =
+ *   2048 / r, at most 8).  A buffer that ends right behind the 256 bytes (sync offset + 256) is
+ *   accepted too: h is then computed by r / 16 CTAs, which is slower for T > 32.
+ *   The sync words must be ZERO before the first
  *   call that uses the buffer (one cudaMemset after allocation) and are left zero by every
  *   call that completes normally, so the buffer can be reused call after call.  Word 2 is a
  *   status word: it becomes 1 if the kernel's bounded wait for h expired (output undefined;
- *   zero the three words before reusing the buffer).  Calls that share a scratch buffer must
+ *   zero the words before reusing the buffer).  Calls that share a scratch buffer must
  *   not overlap on the GPU (use one buffer per stream).
  * Requirements: 1 <= T <= 128, M >= 1 (at most 320 rows per SM), N % 128 == 0, r % 128 == 0.
  * One kernel is launched on `stream` (one CTA per SM; for T <= 16 four extra warps per CTA compute
