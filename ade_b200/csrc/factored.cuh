@@ -833,6 +833,17 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         main_sync();
     }
 
+    // ---- Re-arm the counters for the next call on this scratch buffer.  Every CTA checks out once it is past its
+    // waits, and the last one to do so (nobody reads the counters of this call any more) zeroes them.  Doing it here
+    // rather than at the end keeps two atomic round trips out of the tail of the launch.
+    if (threadIdx.x == 0) {
+        if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {
+            atomicExch(p.sync, 0u);
+            atomicExch(p.sync + 1, 0u);
+            atomicExch(p.sync + 3, 0u);
+        }
+    }
+
     // ---- phase U and store
     if (p.upf > 0) fa_cp_async_wait(0);                    // every thread reads back only its own copies
     int uk = 0;
@@ -853,16 +864,6 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         });
     }
 
-    // ---- the last CTA to finish re-arms the counters for the next call on this scratch buffer
-    main_sync();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {
-            atomicExch(p.sync, 0u);
-            atomicExch(p.sync + 1, 0u);
-            atomicExch(p.sync + 3, 0u);
-        }
-    }
 }
 
 }  // namespace ade
