@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 bulk_commit_group();
             }
         }
-        if (lane == 0) bulk_wait_group<0>();
+        if (lane == 0) bulk_wait_group_read<0>();    // shared memory may go once the last store has read it
     } else if (warp < RS_MMA_WARP) {
         // ------------------------------------------------------------------ unpack
         const int pt = threadIdx.x - RS_EPI_WARPS * 32;
