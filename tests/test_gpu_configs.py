@@ -71,6 +71,30 @@ def test_factored_mlp_modules_long_streams(M, N, r, T):
     assert err <= 1e-2 and cos >= 0.9999, (err, cos)
 
 
+@pytest.mark.parametrize("M,N,r,T", [(4096, 4096, 256, 64), (4096, 4096, 128, 17), (11008, 4096, 512, 128), (4096, 11008, 512, 33),
+                                     (1000, 2048, 1024, 40)])
+def test_delta_only_launch_above_16_tokens(M, N, r, T):
+    """The reference's split (cuBLAS base term + delta kernel) at 17-128 tokens on full-size modules: the launch that
+    slices every phase-A unit over d_i (2048 / r slices, float32 partial sums, second grid-wide step) and stages h
+    and the base term in shared memory.  Also through the module, which takes this route above 16 tokens."""
+    tp = synth.random_packed(M, N, r, 17 * T + r)
+    W_b = synth.base_weight(M, N, 9)
+    x = synth.activations(T, N, 10)
+    p4 = kernels.pack_int4(tp, device=DEV)
+    xd, Wd = x.to(DEV), W_b.to(DEV)
+    y_dense = torch.nn.functional.linear(xd, Wd)
+    y = kernels.decode_forward_packed(xd, y_dense, p4)
+    y2 = kernels.decode_forward_packed(xd, y_dense, p4)
+    torch.cuda.synchronize()
+    assert kernels.factored_status(DEV, T, r) == 0
+    assert torch.equal(y, y2)
+    ref = O.factored_apply(_bits(x), _bits(W_b), O.packed_from_torch(tp))
+    err, cos = O.parity(y.float().cpu().numpy(), ref)
+    assert err <= 1e-2 and cos >= 0.9999, (err, cos)
+    lin = ADEKernelLinear(W_b, tp).to(DEV)
+    assert torch.equal(lin(xd), y)
+
+
 @pytest.mark.parametrize("name,M,N", [("gate", 11008, 4096), ("down", 4096, 11008)])
 def test_config1_reconstructed_mlp(name, M, N):
     """Config 1: Llama-2-7B MLP deltas, r = 512, X 2048 x d_i, reconstructed path."""
