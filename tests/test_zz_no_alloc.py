@@ -22,7 +22,8 @@ def test_static_scratch_entry_matches_the_regular_one():
     dev = "cuda"
     lib = _lib.load()
     stream = torch.cuda.current_stream().cuda_stream
-    for (M, N, r, T) in [(256, 384, 256, 5), (512, 256, 512, 40)]:
+    # the last case is wide enough for the sliced phase A above 16 tokens (four slices of d_i in both entries)
+    for (M, N, r, T) in [(256, 384, 256, 5), (512, 256, 512, 40), (300, 4096, 256, 40)]:
         p4 = kernels.pack_int4(synth.random_packed(M, N, r, seed=M + T), device=dev)
         W = synth.base_weight(M, N, 11).to(dev)
         x = synth.activations(T, N, 12).to(dev)
