@@ -20,20 +20,29 @@ ERRORS = {
     -5: "ADE_ERR_CUDA: a CUDA runtime call failed",
     -6: "ADE_ERR_DEVICE: the current device is not compute capability 10.x",
 }
+# ADE_DEV_* of include/ade_b200.h: what the reconstruction kernels write to *status_dev when a wait expires
 DEVICE_STATUS = {
-    1: "MMA warp timed out waiting for an operand stage",
-    2: "unpack warps timed out waiting for a free operand stage",
-    3: "epilogue timed out waiting for an accumulator",
-    4: "MMA warp timed out waiting for a free accumulator",
-    5: "epilogue timed out waiting for the base-weight tile",
+    1: "ADE_DEV_TIMEOUT_FULL: MMA warp gave up waiting for an operand stage",
+    2: "ADE_DEV_TIMEOUT_EMPTY: unpack warps gave up waiting for a free operand stage",
+    3: "ADE_DEV_TIMEOUT_TMEM_FULL: epilogue gave up waiting for an accumulator",
+    4: "ADE_DEV_TIMEOUT_TMEM_EMPTY: MMA warp gave up waiting for a free accumulator",
+    5: "ADE_DEV_TIMEOUT_SCALES: epilogue gave up waiting for the scale tables of a tile",
+    6: "ADE_DEV_TIMEOUT_BASE: epilogue gave up waiting for its box of w_b",
+    7: "ADE_DEV_TIMEOUT_STRIP_FREE: unpack warps gave up waiting for the resident U strip to retire",
+    8: "ADE_DEV_TIMEOUT_RAW_FULL: unpack warps gave up waiting for packed codes",
+    9: "ADE_DEV_TIMEOUT_STRIP_FULL: MMA warp gave up waiting for the resident U strip",
+    10: "ADE_DEV_TIMEOUT_RAW_EMPTY: load thread gave up waiting for a free raw slot",
+    11: "ADE_DEV_TIMEOUT_SCALES_FREE: scale warp gave up waiting for a free table buffer",
 }
+# ade_b200_set_option
+OPT_WAIT_LIMIT_CYCLES, OPT_COOPERATIVE_LAUNCH, OPT_DROP_SIGNALS = 1, 2, 3
 
 # every symbol include/ade_b200.h declares
 EXPORTS = (
     "ade_b200_device_status", "ade_b200_version", "ade_b200_last_cuda_error",
     "ade_b200_pack_codes", "ade_b200_pack_zeros",
     "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored",
-    "ade_b200_factored_static", "ade_b200_recon",
+    "ade_b200_factored_static", "ade_b200_factored_static_status", "ade_b200_recon", "ade_b200_set_option",
 )
 
 
@@ -81,10 +90,19 @@ def load() -> ctypes.CDLL:
     lib.ade_b200_factored_static.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, ci, vp]
     lib.ade_b200_factored_static.restype = ci
     lib.ade_b200_recon.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp]
+    lib.ade_b200_factored_static_status.argtypes = [vp, ci, vp]
+    lib.ade_b200_factored_static_status.restype = ci
+    lib.ade_b200_set_option.argtypes = [ci, ctypes.c_longlong]
+    lib.ade_b200_set_option.restype = ci
     for name in ("ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_factored", "ade_b200_recon"):
         getattr(lib, name).restype = ci
     _lib = lib
     return lib
+
+
+def set_option(option: int, value: int) -> None:
+    """ade_b200_set_option: wait limit in clock cycles, cooperative launch on / off, diagnostic signal drop."""
+    check(load().ade_b200_set_option(option, value), "ade_b200_set_option")
 
 
 def check(rc: int, what: str) -> None:

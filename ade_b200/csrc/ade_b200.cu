@@ -33,6 +33,11 @@ struct DeviceInfo {
 };
 DeviceInfo g_dev[kMaxDevices];
 
+// process-wide options (ade_b200_set_option)
+long long g_wait_limit = ade::RC_SPIN_LIMIT;   // clock cycles a device-side wait may take before it gives up
+int g_cooperative = 1;                         // factored kernel launched cooperatively (co-residency guaranteed)
+int g_drop_signals = 0;                        // diagnostic: producers inside the kernels stay silent
+
 template <int NT>
 bool optin_factored();
 
@@ -149,11 +154,31 @@ void set_row_split(ade::FactoredParams& p, int grid) {
     p.rows_cap = static_cast<int>(((budget + grid - 1) / grid + 1 + 31) / 32 * 32);
 }
 
+// The factored kernel's CTAs wait for one another (grid-wide counters), so the whole grid has to be resident at
+// once.  A cooperative launch makes the driver guarantee that: the grid starts only when every CTA has an SM, also
+// when other kernels occupy part of the device, and a grid that can never fit is refused at launch.
+template <class Kernel>
+int launch_grid(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t st, const ade::FactoredParams& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_cooperative ? 1 : 0;
+    return cuda_ok(cudaLaunchKernelEx(&cfg, kernel, p)) ? ADE_OK : ADE_ERR_CUDA;
+}
+
 template <int NT, bool FUSE>
 int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
     size_t smem = ade::factored_smem_bytes(NT, p.rows_cap, p.T, p.r);
     p.stages = 0;
     p.upf = 0;
+    p.spin_limit = g_wait_limit;
+    p.drop_arrivals = g_drop_signals;
     // Up to 8 tokens, or up to 16 with a long stream per CTA: W_b goes through a shared-memory FIFO (deeper than
     // registers allow).  At 9-16 tokens a short stream (a 4096 x 4096 module is 227 KB per CTA) is as fast with the
     // register prefetch: the deep FIFO raises the loaded memory latency, which the h hand-over pays several times.
@@ -180,12 +205,10 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
     }
     if constexpr (FUSE && ade::fa_side(NT)) {
         if (p.stages >= 2) {
-            ade::factored_kernel<NT, true, true><<<grid, ade::fa_threads(NT), smem, st>>>(p);
-            return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+            return launch_grid(ade::factored_kernel<NT, true, true>, grid, ade::fa_threads(NT), smem, st, p);
         }
     }
-    ade::factored_kernel<NT, FUSE><<<grid, ade::fa_threads(NT), smem, st>>>(p);
-    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    return launch_grid(ade::factored_kernel<NT, FUSE>, grid, ade::fa_threads(NT), smem, st, p);
 }
 
 template <int NT>
@@ -221,10 +244,26 @@ int set_blocks(ade::FactoredParams& p, const ade_delta_t* d) {
 }
 
 // ---- scratch of ade_b200_factored_static: lives in the library image, one copy per GPU that loads it.
-// Layout: 256 bytes holding the kernel's three sync words (always at the same place, whatever T and r),
-// then h = V^T x (bf16, T x r).  In host code this name is only a handle for cudaGetSymbolAddress.
+// Layout: 256 bytes of control words (words 0-3: the kernel's sync words, cleared before every launch; word 4:
+// the status word, which only ade_b200_factored_static_status clears), always at the same place whatever T and
+// r, then h = V^T x and, above 16 tokens, the partial sums of sliced phase-A units in what is left.  In host
+// code this name is only a handle for cudaGetSymbolAddress.
 __device__ __align__(256) unsigned char g_static_scratch[ADE_B200_STATIC_SCRATCH_BYTES];
 void* g_static_scratch_addr[kMaxDevices] = {};
+
+// Device address of the array on the current device; looked up on the first use per device.
+int static_scratch_base(char** out) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return ADE_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return ADE_ERR_DEVICE;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* addr = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&addr, g_static_scratch)) || addr == nullptr) return ADE_ERR_CUDA;
+        g_static_scratch_addr[dev] = addr;
+    }
+    *out = static_cast<char*>(g_static_scratch_addr[dev]);
+    return ADE_OK;
+}
 
 }  // namespace
 
@@ -318,6 +357,7 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
     p.vz = d->vz;
     p.h = static_cast<__nv_bfloat16*>(scratch);
     p.sync = reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + ade_b200_factored_sync_offset(T, d->r));
+    p.status = p.sync + 2;
     p.parts = factored_parts(T, d->r, d->N, scratch_bytes, w_b != nullptr);
     p.hpart = reinterpret_cast<float*>(static_cast<char*>(scratch) + factored_scratch_min(T, d->r));
     p.out = static_cast<__nv_bfloat16*>(out);
@@ -353,18 +393,13 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     const DeviceInfo* di = nullptr;
     rc = device_info(&di);
     if (rc) return rc;
-    int dev = 0;
-    if (!cuda_ok(cudaGetDevice(&dev))) return ADE_ERR_CUDA;
-    if (g_static_scratch_addr[dev] == nullptr) {
-        // first call on this device (it is the current one): turn the symbol into a device address
-        void* addr = nullptr;
-        if (!cuda_ok(cudaGetSymbolAddress(&addr, g_static_scratch)) || addr == nullptr) return ADE_ERR_CUDA;
-        g_static_scratch_addr[dev] = addr;
-    }
-    char* base = static_cast<char*>(g_static_scratch_addr[dev]);
+    char* base = nullptr;
+    rc = static_scratch_base(&base);
+    if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // the array keeps whatever the previous call left: the sync words must start at zero
-    if (!cuda_ok(cudaMemsetAsync(base, 0, 256, st))) return ADE_ERR_CUDA;
+    // the array keeps whatever the previous call left: the four sync words must start at zero (the status word
+    // behind them is sticky until ade_b200_factored_static_status clears it)
+    if (!cuda_ok(cudaMemsetAsync(base, 0, 16, st))) return ADE_ERR_CUDA;
     ade::FactoredParams p;
     p.w_b = static_cast<const __nv_bfloat16*>(w_b);
     p.x = static_cast<const __nv_bfloat16*>(x);
@@ -376,6 +411,7 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     p.vs = d->vs;
     p.vz = d->vz;
     p.sync = reinterpret_cast<unsigned int*>(base);
+    p.status = p.sync + 4;
     p.h = reinterpret_cast<__nv_bfloat16*>(base + 256);
     {
         // what is left of the array behind h takes the partial sums of sliced phase-A units (T > 16)
@@ -399,6 +435,34 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     if (T <= 32) return launch_factored<4>(p, grid, st);
     if (T <= 64) return launch_factored<8>(p, grid, st);
     return launch_factored<16>(p, grid, st);
+}
+
+int ade_b200_factored_static_status(int* dst, int clear, void* stream) {
+    if (!dst) return ADE_ERR_NULL;
+    char* base = nullptr;
+    const int rc = static_scratch_base(&base);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!cuda_ok(cudaMemcpyAsync(dst, base + 16, sizeof(int), cudaMemcpyDefault, st))) return ADE_ERR_CUDA;
+    if (clear && !cuda_ok(cudaMemsetAsync(base + 16, 0, sizeof(int), st))) return ADE_ERR_CUDA;
+    return ADE_OK;
+}
+
+int ade_b200_set_option(int option, long long value) {
+    switch (option) {
+        case ADE_OPT_WAIT_LIMIT_CYCLES:
+            if (value < 0) return ADE_ERR_SHAPE;
+            g_wait_limit = value == 0 ? ade::RC_SPIN_LIMIT : value;
+            return ADE_OK;
+        case ADE_OPT_COOPERATIVE_LAUNCH:
+            g_cooperative = value != 0;
+            return ADE_OK;
+        case ADE_OPT_DROP_SIGNALS:
+            g_drop_signals = value != 0;
+            return ADE_OK;
+        default:
+            return ADE_ERR_SHAPE;
+    }
 }
 
 int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* dbg_acc, int* status_dev,
@@ -427,6 +491,8 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     p.N = d->N;
     p.r = d->r;
     p.one = 1.0f;
+    p.spin_limit = g_wait_limit;
+    p.drop_loads = g_drop_signals;
     const int ng = d->r / ADE_B200_GROUP;
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;

@@ -46,7 +46,7 @@ __device__ __forceinline__ void main_sync() { asm volatile("bar.sync 1, %0;" ::"
 __device__ __forceinline__ void side_sync() { asm volatile("bar.sync 2, %0;" ::"n"(FA_SIDE_WARPS * 32) : "memory"); }
 constexpr int FA_ROWS = 32;                    // output rows per pass (two m16 tiles per warp)
 constexpr uint32_t kBf2_128 = 0x43004300u;     // bf16x2 (128, 128)
-constexpr long long FA_SPIN_LIMIT = 2000000000LL;   // clock cycles (about one second)
+constexpr long long FA_SPIN_LIMIT = 2000000000LL;   // default limit of a grid-wide wait in clock cycles (about one second)
 
 struct FactoredParams {
     const __nv_bfloat16* w_b;      // [M][N] or nullptr
@@ -62,6 +62,9 @@ struct FactoredParams {
     float* hpart;                  // scratch, T > 16 and parts > 1: float32 [parts][T][r] partial sums of h
     int parts;                     // T > 16: every 16-rank unit of phase A is split over this many slices of d_i
     unsigned int* sync;            // scratch: [0] units arrived, [1] CTAs done, [2] status (0 = ok), [3] slices of h reduced
+    unsigned int* status;          // where an expired wait records 1: sync + 2, or a word that outlives the call's memset
+    long long spin_limit;          // clock cycles after which a grid-wide wait gives up
+    int drop_arrivals;             // diagnostic: phase-A units do not report, so that the wait for h runs out
     __nv_bfloat16* out;            // [T][M]
     int T, M, N, r;
     int rows_cap;                  // rows of the y buffer in shared memory (multiple of 32)
@@ -701,7 +704,7 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         }
         // xv_unit ended with a barrier of the side warps; the release orders their stores of h before the count.
         // One fire-and-forget instruction: a fence and an atomic would be two more memory round trips under load.
-        if (done && threadIdx.x == FA_THREADS) red_release_gpu_add(p.sync, done);
+        if (done && threadIdx.x == FA_THREADS && !p.drop_arrivals) red_release_gpu_add(p.sync, done);
         return;
     }
     if (!SIDE) {
@@ -712,7 +715,7 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
                                   parts > 1 ? p.hpart + static_cast<size_t>(part) * p.T * p.r : nullptr, warp, gid, tig);
             ++done;
         }
-        if (done && threadIdx.x == 0) {                    // xv_unit ended with a barrier of the main warps
+        if (done && threadIdx.x == 0 && !p.drop_arrivals) {   // xv_unit ended with a barrier of the main warps
             __threadfence();
             atomicAdd(p.sync, done);
         }
@@ -752,8 +755,8 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     if (threadIdx.x == 0) {
         const long long t0 = clock64();
         while (ld_acquire_gpu(p.sync) < static_cast<unsigned int>(n_units)) {
-            if (clock64() - t0 > FA_SPIN_LIMIT) {
-                atomicExch(p.sync + 2, 1u);
+            if (clock64() - t0 > p.spin_limit) {
+                atomicExch(p.status, 1u);
                 break;
             }
         }
@@ -787,8 +790,8 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
             red_release_gpu_add(p.sync + 3, 1u);
             const long long t0 = clock64();
             while (ld_acquire_gpu(p.sync + 3) < static_cast<unsigned int>(G)) {
-                if (clock64() - t0 > FA_SPIN_LIMIT) {
-                    atomicExch(p.sync + 2, 1u);
+                if (clock64() - t0 > p.spin_limit) {
+                    atomicExch(p.status, 1u);
                     break;
                 }
             }

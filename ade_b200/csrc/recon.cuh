@@ -41,7 +41,7 @@ constexpr int RC_THREADS = RC_EPI_THREADS + RC_PROD_THREADS + 32;
 constexpr int RC_TMEM_COLS = 256;
 constexpr int RC_RAW_DEPTH = 3;                         // raw code items in flight per unpack thread
 constexpr int RC_RAW_ITEM = RC_PROD_THREADS * (8 * 16 + 8 * 4);   // per item: 8 x 16 B codes + 8 x 4 B zero words
-constexpr long long RC_SPIN_LIMIT = 2000000000LL;       // clock cycles (about one second)
+constexpr long long RC_SPIN_LIMIT = 2000000000LL;       // default limit of a wait in clock cycles (about one second)
 // instruction descriptor: D = S32 (bits 4-5 = 2), A = B = signed 8-bit (bits 7-9, 10-12 = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 = 16 (bits 17-22), M >> 4 = 8 (bits 24-28)
 // Every INT32 accumulator starts a group at the bit pattern of the float 1.5 * 2^23, so that after the
@@ -63,6 +63,15 @@ struct ReconParams {
     int* status;
     int M, N, r;
     float one;      // 1.0f, set by the host: a value the assembler cannot fold (see recon_strip.cuh)
+    long long spin_limit;   // clock cycles after which a wait gives up (RC_SPIN_LIMIT unless the host lowered it)
+    int drop_loads;         // diagnostic: the code loads are not issued, so that the waits for them run out
+};
+
+// what a bounded wait needs to give up: the CTA's abort flag, the caller's status word, the cycle limit
+struct WaitCtx {
+    volatile int* abort_flag;
+    int* status;
+    long long limit;
 };
 
 constexpr int RC_WB_ROW = 272;                          // one tile row: 256 bytes of bf16, padded (bank spread)
@@ -74,19 +83,26 @@ __host__ __device__ inline size_t recon_smem_bytes(int ng) {
            static_cast<size_t>(2) * ng * RC_TILE * (sizeof(float) + sizeof(uint16_t)) + 256;
 }
 
-__device__ __forceinline__ void wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                             int code) {
+__device__ __forceinline__ void wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         __nanosleep(64);                                  // leave the issue slots to the warps that have work
-        if (*abort_flag) return;
-        if (clock64() - t0 > RC_SPIN_LIMIT) {
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
+        if (*w.abort_flag) return;
+        if (clock64() - t0 > w.limit) {
+            *w.abort_flag = 1;
+            if (w.status) atomicCAS(w.status, 0, code);
             return;
         }
     }
+}
+
+// After an expired wait the roles run on without waiting for one another.  Before the CTA gives up its shared
+// and tensor memory, let whatever is still in flight (tensor-map copies into shared memory, queued MMAs) land:
+// a bounded sleep, far longer than any of them takes.
+__device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
+    if (*abort_flag)
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
 }
 
 // cp.async with zero fill: copies 16 (or 4) bytes when live, writes zeros otherwise
@@ -186,6 +202,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
 
     const int tiles_n = p.N >> 7;
     const int ntiles = ((p.M + RC_TILE - 1) >> 7) * tiles_n;
+    const WaitCtx wctx{abort_flag, p.status, p.spin_limit};
 
     if (warp < RC_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
@@ -273,7 +290,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                wait_bounded(tfull0 + 8 * a, aph, abort_flag, p.status, 3);
+                wait_bounded(tfull0 + 8 * a, aph, wctx, 3);
                 tc_fence_after();
                 const float u = su[g * RC_TILE + row];
                 const uint64_t uu = f2_pack(u, u);
@@ -349,7 +366,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
         const int pt = threadIdx.x - RC_EPI_THREADS;
         const int c = pt & 3, rbase = pt >> 2;
         const int my_tiles = static_cast<int>(blockIdx.x) < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const int total = my_tiles * ng;
+        const int total = p.drop_loads ? 0 : my_tiles * ng;   // diagnostic: no items, the MMA thread's wait runs out
         const size_t step = static_cast<size_t>(32) * (p.r >> 1);          // 32 rows further down a code array
         const uint32_t raw_s = smem_u32(raw_ring);
         ProdCursor ld, use;                               // issue position and consume position
@@ -409,7 +426,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
             advance(use);
             issue(idx + RC_RAW_DEPTH - 1);               // refill the slot consumed one iteration ago
             const uint32_t s = idx % RC_STAGES, ph = (idx / RC_STAGES) & 1;
-            wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 2);
+            wait_bounded(empty0 + 8 * s, ph ^ 1, wctx, 2);
             uint8_t* A = stage_base + s * RC_STAGE_BYTES;
             uint8_t* B = A + RC_TILE * 128;
 #pragma unroll
@@ -430,8 +447,8 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t s = it % RC_STAGES, ph = (it / RC_STAGES) & 1;
                     const uint32_t a = it & 1, aph = (it >> 1) & 1;
-                    wait_bounded(tempty0 + 8 * a, aph, abort_flag, p.status, 4);   // use u of a stage waits for its u-th release
-                    wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, 1);
+                    wait_bounded(tempty0 + 8 * a, aph, wctx, 4);   // use u of a stage waits for its u-th release
+                    wait_bounded(full0 + 8 * s, ph, wctx, 1);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(stage_base + s * RC_STAGE_BYTES);
                     const uint64_t ad = smem_desc_k_sw128(sa);
@@ -447,6 +464,7 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
         __syncwarp();
     }
 
+    drain_after_abort(abort_flag);
     tc_fence_before();
     __syncthreads();
     if (warp == RC_MMA_WARP) tmem_dealloc(tmem_base, RC_TMEM_COLS);

@@ -71,7 +71,7 @@ struct RsCfg {
     static constexpr int BAR_SC_EMPTY = BAR_SC_FULL + 2;
     static constexpr int BAR_WB = BAR_SC_EMPTY + 2;
     static constexpr int BAR_COUNT = BAR_WB + WB_BUFS * RS_EPI_WARPS;
-    static constexpr size_t smem_bytes(int ng) {
+    __host__ __device__ static constexpr size_t smem_bytes(int ng) {
         return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(B_STAGES) * RS_OPER_BYTES +
                WB_BYTES + static_cast<size_t>(RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + BAR_COUNT * 8 + 16;
     }
@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
     const int ntiles = ((p.M + RC_TILE - 1) >> 7) * tiles_n;
     const int t_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
     const int t_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
+    const WaitCtx wctx{abort_flag, p.status, p.spin_limit};
 
     if (warp < RS_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
                 tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
             }
-            wait_bounded(bar(C::BAR_SC_FULL + b), jph, abort_flag, p.status, 5);
+            wait_bounded(bar(C::BAR_SC_FULL + b), jph, wctx, 5);
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);          // this tile's tables
 
             uint64_t acc[16];
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                wait_bounded(bar(C::BAR_TFULL + a), aph, abort_flag, p.status, 3);
+                wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
                 tc_fence_after();
                 const uint32_t scg = sct + g * RS_SC_BYTES;
                 const float u = __uint_as_float(lds4(scg + row * 4));
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::BAR_SC_EMPTY + b));             // this warp is done with the scale tables
-            wait_bounded(wbar, wph, abort_flag, p.status, 6);
+            wait_bounded(wbar, wph, wctx, 6);
             uint4 wv4[4];                                // 8 columns per 16-byte chunk
 #pragma unroll
             for (int c = 0; c < 4; ++c) wv4[c] = lds16(box + own + ((c ^ swz) << 4));
@@ -296,10 +297,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                         for (int g = 0; g < ng; ++g) z |= static_cast<uint64_t>(p.uz[static_cast<size_t>(m) * ng + g]) << (8 * g);
                     za_pack[i] = z;
                 }
-                if (sk > 0) wait_bounded(bar(C::BAR_A_FREE), (sk - 1) & 1, abort_flag, p.status, 7);   // old strip's MMAs retired
+                if (sk > 0) wait_bounded(bar(C::BAR_A_FREE), (sk - 1) & 1, wctx, 7);   // old strip's MMAs retired
                 for (int g = 0; g < ng; ++g, ++ri) {
                     const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
-                    wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                    wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, wctx, 8);
                     const uint32_t rs = rawr + slot * RS_RAW_SLOT;
                     uint4 qa[4];
 #pragma unroll
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
             for (int g = 0; g < ng; ++g, ++ri, ++bi) {
                 const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
-                wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, abort_flag, p.status, 8);
+                wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, wctx, 8);
                 const uint32_t rs = rawr + slot * RS_RAW_SLOT;
                 uint4 qb[4];
                 uint32_t zb[4];
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(C::BAR_RAW_EMPTY + slot));
                 const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
-                wait_bounded(bar(C::BAR_B_EMPTY + s), bph ^ 1, abort_flag, p.status, 2);
+                wait_bounded(bar(C::BAR_B_EMPTY + s), bph ^ 1, wctx, 2);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) unpack_store_s(b_st + s * RS_OPER_BYTES, rbase + 32 * i, c, qb[i], zb[i]);
                 fence_proxy_async_smem();
@@ -347,9 +348,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 for (int g = 0; g < ng; ++g, ++it, ++bi) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                     const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
-                    wait_bounded(bar(C::BAR_TEMPTY + a), aph, abort_flag, p.status, 4);
-                    wait_bounded(bar(C::BAR_B_FULL + s), bph, abort_flag, p.status, 1);
-                    if (first) wait_bounded(bar(C::BAR_A_FULL + g), k & 1, abort_flag, p.status, 9);
+                    wait_bounded(bar(C::BAR_TEMPTY + a), aph, wctx, 4);
+                    wait_bounded(bar(C::BAR_B_FULL + s), bph, wctx, 1);
+                    if (first) wait_bounded(bar(C::BAR_A_FULL + g), k & 1, wctx, 9);
                     tc_fence_after();
                     const uint64_t ad = smem_desc_k_sw128(a_res + g * RS_OPER_BYTES);
                     const uint64_t bd = smem_desc_k_sw128(b_st + s * RS_OPER_BYTES);
@@ -366,7 +367,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         __syncwarp();
     } else if (warp == RS_LOAD_WARP) {
         // ------------------------------------------------------------------ packed codes -> raw ring
-        if (lane == 0) {
+        if (lane == 0 && !p.drop_loads) {                   // diagnostic drop_loads: nothing arrives, the waits run out
             prefetch_tensormap(&maps.uq);
             prefetch_tensormap(&maps.vq);
             uint32_t ri = 0;
@@ -377,14 +378,14 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     cur_strip = strip;
                     for (int g = 0; g < ng; ++g, ++ri) {
                         const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
-                        wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                        wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, wctx, 10);
                         mbar_arrive_expect_tx(bar(C::BAR_RAW_FULL + slot), RS_RAW_CODES);
                         tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.uq, g * 64, strip << 7, bar(C::BAR_RAW_FULL + slot));
                     }
                 }
                 for (int g = 0; g < ng; ++g, ++ri) {
                     const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
-                    wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, abort_flag, p.status, 10);
+                    wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, wctx, 10);
                     mbar_arrive_expect_tx(bar(C::BAR_RAW_FULL + slot), RS_RAW_CODES + 128);
                     tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.vq, g * 64, n0, bar(C::BAR_RAW_FULL + slot));
                     bulk_g2s(rawr + slot * RS_RAW_SLOT + RS_RAW_CODES, p.vz + static_cast<size_t>(g) * p.N + n0, 128,
@@ -422,7 +423,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     vv[t] = ldg16(p.vs + static_cast<size_t>(vi >> 4) * p.N + n0 + (vi & 15) * 8);
                 }
             }
-            wait_bounded(bar(C::BAR_SC_EMPTY + b), jph ^ 1, abort_flag, p.status, 11);
+            wait_bounded(bar(C::BAR_SC_EMPTY + b), jph ^ 1, wctx, 11);
 #pragma unroll
             for (int t = 0; t < NV; ++t) {
                 const int vi = lane + 32 * t;
@@ -446,6 +447,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         }
     }
 
+    drain_after_abort(abort_flag);
     tc_fence_before();
     __syncthreads();
     if (warp == RS_MMA_WARP) tmem_dealloc(tmem_base, RS_TMEM_COLS);

@@ -94,14 +94,16 @@ def pack_int4(packed: dict, group_size: int = GROUP, device=None) -> dict:
     if group_size != GROUP:
         raise ValueError("the kernels are specialised for group size 128")
     dev = torch.device(device) if device is not None else packed["U_codes"].device
-    uc = packed["U_codes"].to(dev, torch.uint8)
-    vc = packed["Vt_codes"].to(dev, torch.uint8)
-    M, r = uc.shape
-    r2, N = vc.shape
+    M, r = packed["U_codes"].shape
+    r2, N = packed["Vt_codes"].shape
     if r != r2 or r % GROUP:
         raise ValueError(f"pack_int4: rank {r} / {r2} must match and be a multiple of {GROUP}")
     if N % 8:
         raise ValueError(f"pack_int4: d_i = {N} must be a multiple of 8")
+    if dev.type == "cuda":
+        return _pack_int4_cuda(packed, dev)
+    uc = packed["U_codes"].to(dev, torch.uint8)
+    vc = packed["Vt_codes"].to(dev, torch.uint8)
     out = {
         "uq": pack_nibbles(uc),
         "vq": pack_nibbles(vc.t().contiguous()),
@@ -112,6 +114,52 @@ def pack_int4(packed: dict, group_size: int = GROUP, device=None) -> dict:
         "vz": packed["Vt_zero"].to(dev).to(torch.float32).to(torch.uint8).contiguous(),
         "M": M, "N": N, "r": r,
     }
+    return out
+
+
+_loaders: dict = {}
+
+
+def _pack_int4_cuda(packed: dict, dev: torch.device) -> dict:
+    """Stored form built by the packing kernels of the C ABI.  Fields that live on the CPU go through the pinned
+    staging path of ``packed_io.DeviceDeltaLoader`` (one copy, then kernels); fields already on the device are
+    packed where they are, on the current stream."""
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    if all(packed[k].device.type == "cpu" for k in ("U_codes", "Vt_codes", "U_scale", "U_zero", "Vt_scale", "Vt_zero")):
+        from .packed_io import DeviceDeltaLoader
+
+        loader = _loaders.get(dev.index)
+        if loader is None:
+            loader = _loaders[dev.index] = DeviceDeltaLoader(dev)
+        out = loader.load(packed)
+        loader.finish()
+        return out
+    lib = _lib.load()
+    uc = packed["U_codes"].to(dev, torch.uint8).contiguous()
+    vc = packed["Vt_codes"].to(dev, torch.uint8).contiguous()
+    uzb = packed["U_zero"].to(dev, torch.bfloat16).contiguous()
+    vzb = packed["Vt_zero"].to(dev, torch.bfloat16).contiguous()
+    M, r = uc.shape
+    N = vc.shape[1]
+    ng = r // GROUP
+    out = {
+        "uq": torch.empty(M, r // 2, dtype=torch.uint8, device=dev),
+        "vq": torch.empty(N, r // 2, dtype=torch.uint8, device=dev),
+        "vt": torch.empty(r, N // 2, dtype=torch.uint8, device=dev),
+        "us": packed["U_scale"].to(dev, torch.bfloat16).contiguous(),
+        "uz": torch.empty(M, ng, dtype=torch.uint8, device=dev),
+        "vs": packed["Vt_scale"].to(dev, torch.bfloat16).contiguous(),
+        "vz": torch.empty(ng, N, dtype=torch.uint8, device=dev),
+        "M": M, "N": N, "r": r,
+    }
+    with _on_device(dev):
+        sp = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.ade_b200_pack_codes(uc.data_ptr(), out["uq"].data_ptr(), M, r, 0, sp), "ade_b200_pack_codes(U)")
+        _lib.check(lib.ade_b200_pack_codes(vc.data_ptr(), out["vt"].data_ptr(), r, N, 0, sp), "ade_b200_pack_codes(Vt)")
+        _lib.check(lib.ade_b200_pack_codes(vc.data_ptr(), out["vq"].data_ptr(), N, r, 1, sp), "ade_b200_pack_codes(V)")
+        _lib.check(lib.ade_b200_pack_zeros(uzb.data_ptr(), out["uz"].data_ptr(), M * ng, sp), "ade_b200_pack_zeros(U)")
+        _lib.check(lib.ade_b200_pack_zeros(vzb.data_ptr(), out["vz"].data_ptr(), ng * N, sp), "ade_b200_pack_zeros(Vt)")
     return out
 
 
@@ -156,6 +204,30 @@ def _scratch_for(dev: torch.device, stream_ptr: int, T: int, r: int, nbytes: int
     if buf is None:
         buf = _scratch[key] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
     return buf
+
+
+def check_factored_status(dev=None) -> None:
+    """Raise if any factored launch on `dev` (default: every device) recorded an expired wait for h in its
+    scratch buffer: the output of that launch was undefined.  Synchronises the devices it looks at, so it belongs
+    at the end of a generation or a benchmark, not between launches."""
+    lib = _lib.load()
+    index = None if dev is None else (torch.device(dev).index if torch.device(dev).index is not None else torch.cuda.current_device())
+    for (di, stream_ptr, T, r), buf in list(_scratch.items()):
+        if index is not None and di != index:
+            continue
+        off = lib.ade_b200_factored_sync_offset(T, r)
+        if int(buf[off:off + 12].view(torch.int32)[2].item()) != 0:
+            raise _lib.AdeKernelError(
+                f"factored kernel on cuda:{di} (T={T}, r={r}): the grid-wide wait for h = V^T x expired; the output of "
+                "that launch is undefined (zero the scratch buffer's sync words before reusing it)")
+
+
+def reset_factored_scratch(dev=None) -> None:
+    """Zero the sync words of the cached scratch buffers (after a launch whose wait expired)."""
+    index = None if dev is None else (torch.device(dev).index if torch.device(dev).index is not None else torch.cuda.current_device())
+    for (di, _, _, _), buf in _scratch.items():
+        if index is None or di == index:
+            buf.zero_()
 
 
 def factored_status(dev, T: int, r: int, stream_ptr: int | None = None) -> int:

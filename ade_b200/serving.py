@@ -36,15 +36,19 @@ class ADEKernelLinear(nn.Module):
 
     def __init__(self, W_b: torch.Tensor, packed: dict, group_size: int = GROUP,
                  decode_max_tokens: int = 128, use_decode: bool = True, use_recon: bool = True,
-                 split_k: bool = False):
+                 split_k: bool = False, stored: dict | None = None):
         """
         Parameters:
             W_b: Base weight (d_o, d_i).
-            packed: Packed factors of the module (src/quantization.py:276-285 layout).
+            packed: Packed factors of the module (src/quantization.py:276-285 layout); may be None when
+                `stored` is given.
             group_size: Group size G (128).
             decode_max_tokens: Largest T handled by factored application (at most 128).
             use_decode / use_recon: must stay True; there is no float reconstruction fallback.
             split_k: accepted for compatibility, ignored (the kernels are deterministic).
+            stored: the module's stored form if it has been built already (``pack_int4`` or
+                ``packed_io.DeviceDeltaLoader.load``); the module then packs nothing itself and its buffers live
+                where the stored form lives.  No counterpart in the reference.
         """
         super().__init__()
         if not (use_decode and use_recon):
@@ -56,8 +60,11 @@ class ADEKernelLinear(nn.Module):
         self.decode_max_tokens = int(decode_max_tokens)
         self.use_decode, self.use_recon, self.split_k = use_decode, use_recon, split_k
         self.out_features, self.in_features = W_b.shape
-        self.register_buffer("weight", W_b.detach().to(torch.bfloat16).contiguous())
-        p4 = pack_int4(packed, group_size)
+        p4 = stored if stored is not None else pack_int4(packed, group_size)
+        if (p4["M"], p4["N"]) != tuple(W_b.shape):
+            raise ValueError(f"delta is {p4['M']} x {p4['N']}, base weight {tuple(W_b.shape)}")
+        W_b = W_b.detach().to(device=p4["uq"].device, dtype=torch.bfloat16) if stored is not None else W_b.detach().to(torch.bfloat16)
+        self.register_buffer("weight", W_b.contiguous())
         self._dims = (p4["M"], p4["N"], p4["r"])
         for k in STORED_KEYS:
             self.register_buffer(f"p4_{k}", p4[k])
@@ -146,26 +153,38 @@ class FusedADEGroup:
             # rows of member i use only its own rank groups: the kernel skips the zero blocks of U
             "blocks": [(self.offsets[i], sum(rs[:i]) // GROUP) for i in range(len(Ms) + 1)] if len(Ms) <= 4 else None,
         }
-        self._key = None
+        self._x = None                # the input tensor the cached result belongs to (kept alive while cached)
+        self._ver = -1
         self._y = None
         self._used = set()
         for i, m in enumerate(self.members):
             m._group = (self, i)
 
+    def release(self):
+        """Dissolve the group: the members go back to their own launches and the fused buffers are dropped."""
+        for m in self.members:
+            if m._group is not None and m._group[0] is self:
+                m._group = None
+        self.weight = self.p4 = self._x = self._y = None
+
     def apply(self, index: int, x, x2):
         """Output of member `index` for the input x (x2 = x as a contiguous (T, d_i) bfloat16 matrix), or None when
-        the group cannot serve it (the members moved to another device since the group was built)."""
-        if self.members[0].weight.data_ptr() != self.weight.data_ptr():
+        the group cannot serve it (the members moved to another device since the group was built; the group then
+        dissolves).  The first member asked about a given tensor launches for all; the others get their slices of
+        that result as long as they present the very same tensor object, unmodified: the group holds a reference to
+        it while a result is cached, so no other tensor can take its place in memory, and an in-place write bumps
+        its version."""
+        if self.weight is None or self.members[0].weight.data_ptr() != self.weight.data_ptr():
+            self.release()
             return None
-        key = (x.data_ptr(), tuple(x.shape), x._version, x.dtype)
-        if self._y is None or key != self._key or index in self._used:
+        if self._y is None or x is not self._x or x._version != self._ver or index in self._used:
             self._y = factored_forward(x2, self.p4, weight=self.weight)
-            self._key = key
+            self._x, self._ver = x, x._version
             self._used = set()
         self._used.add(index)
         y = self._y[:, self.offsets[index]:self.offsets[index + 1]]
         if len(self._used) == len(self.members):
-            self._y = None                     # every member has taken its slice: nothing is served twice
+            self._x = self._y = None           # every member has taken its slice: nothing is served twice
         return y
 
 
@@ -198,36 +217,52 @@ def fuse_kernel_linears(model, max_rank: int = 2048) -> int:
 
 
 def _decoder_layers(model):
-    """Decoder layers of a LLaMA-family causal LM or of a llava-hf LLaVA model (src/serving.py:115-130)."""
-    lm = getattr(getattr(model, "model", None), "language_model", None)
-    if lm is None:
-        lm = getattr(model, "language_model", None)
-    if lm is not None:
-        return getattr(lm, "model", lm).layers
-    return model.model.layers
+    """The ``nn.ModuleList`` of decoder layers, wherever the architecture keeps it: a LLaMA-family causal LM
+    (``model.model.layers``) or a llava-hf LLaVA model, whose language model sits under ``model.language_model``
+    or, in newer transformers, ``model.model.language_model`` (what src/serving.py:115-130 resolves)."""
+    for path in ("model.language_model.model", "model.language_model", "language_model.model", "language_model", "model"):
+        node = model
+        for name in path.split("."):
+            node = getattr(node, name, None)
+            if node is None:
+                break
+        if node is not None and isinstance(getattr(node, "layers", None), nn.ModuleList):
+            return node.layers
+    raise AttributeError(f"{type(model).__name__} has no decoder layer list this build knows how to find")
 
 
-def attach_kernel_linears(model, base_state_dict: dict, per_module: dict, group_size: int = GROUP,
-                          decode_max_tokens: int = 128, split_k: bool = False) -> int:
-    """Replace every linear module that has a packed delta by an ADEKernelLinear, in place.
+def attach_kernel_linears(model, base_state_dict: dict, per_module, group_size: int = GROUP,
+                          decode_max_tokens: int = 128, split_k: bool = False, device=None) -> int:
+    """Give every linear module that has a packed delta an ADEKernelLinear in its place.
 
-    The loop of src/serving.py:178-190 for a model that is already in memory: `base_state_dict`
-    maps ``model.layers.<i>.<name>.weight`` to the base weight, `per_module` maps
-    ``model.layers.<i>.<name>`` to its packed dict.  Returns the number of modules replaced.
+    Does for a model that is already in memory what the module-swap loop of src/serving.py:178-190 does after
+    loading one: `base_state_dict` maps ``model.layers.<i>.<name>.weight`` to the base weight, `per_module` (a
+    dict or a ``packed_io.PackedDeltaFile``) maps ``model.layers.<i>.<name>`` to the packed fields.  With a CUDA
+    `device` the stored forms are built there in one pass (pinned staging + the packing kernels, see
+    ``packed_io.DeviceDeltaLoader``) and the new modules are born on that device; otherwise they are packed on
+    the CPU and move with ``model.to``.  Returns the number of modules replaced.
     """
-    layers = _decoder_layers(model)
-    n = 0
-    for li in range(len(layers)):
-        for sn in LINEAR_MODULE_NAMES:
-            prefix = f"model.layers.{li}.{sn}"
+    loader = None
+    if device is not None and torch.device(device).type == "cuda":
+        from .packed_io import DeviceDeltaLoader
+
+        loader = DeviceDeltaLoader(device)
+    fetch = per_module.module if hasattr(per_module, "module") else per_module.__getitem__
+    swapped = 0
+    for li, layer in enumerate(_decoder_layers(model)):
+        for sub in LINEAR_MODULE_NAMES:
+            prefix = f"model.layers.{li}.{sub}"
             if prefix not in per_module:
                 continue
-            parts = sn.split(".")
-            parent = layers[li].get_submodule(".".join(parts[:-1]))
-            setattr(parent, parts[-1], ADEKernelLinear(base_state_dict[prefix + ".weight"], per_module[prefix],
-                                                       group_size, decode_max_tokens, split_k=split_k))
-            n += 1
-    return n
+            owner_path, _, leaf = sub.rpartition(".")
+            stored = loader.load(fetch(prefix)) if loader is not None else None
+            new = ADEKernelLinear(base_state_dict[prefix + ".weight"], None if loader is not None else fetch(prefix),
+                                  group_size, decode_max_tokens, split_k=split_k, stored=stored)
+            setattr(layer.get_submodule(owner_path), leaf, new)
+            swapped += 1
+    if loader is not None:
+        loader.finish()
+    return swapped
 
 
 def build_kernel_model(task: str, aligned_path: str, base_path: str, packed_path: str,
@@ -241,7 +276,7 @@ def build_kernel_model(task: str, aligned_path: str, base_path: str, packed_path
     """
     from transformers import AutoModelForCausalLM, AutoProcessor, AutoTokenizer
 
-    from .packed_io import load_packed
+    from .packed_io import PackedDeltaFile
 
     for ok, reason in (decode_kernel_status(device), recon_kernel_status(device)):
         if not ok:
@@ -254,9 +289,130 @@ def build_kernel_model(task: str, aligned_path: str, base_path: str, packed_path
         model = AutoModelForCausalLM.from_pretrained(aligned_path, dtype=torch.bfloat16)
         processor = AutoTokenizer.from_pretrained(aligned_path)
     base_sd = AutoModelForCausalLM.from_pretrained(base_path, dtype=torch.bfloat16).state_dict()
-    per_module, meta = load_packed(packed_path)
-    n = attach_kernel_linears(model, base_sd, per_module, int(meta["group_size"]), decode_max_tokens, split_k)
-    del base_sd, per_module
+    delta = PackedDeltaFile(packed_path)                       # memory-mapped; streamed to the device module by module
+    n = attach_kernel_linears(model, base_sd, delta, int(delta.meta["group_size"]), decode_max_tokens, split_k, device=device)
+    del base_sd, delta
     model = model.to(device).eval()
     print(f"[kernels] {n} linear modules apply the compressed delta at every forward")
     return model, processor
+
+
+class GreedyGraphDecoder:
+    """Greedy generation whose per-token step is one CUDA-graph replay.
+
+    The reference generates with Hugging Face ``model.generate(..., do_sample=False)`` (src/evaluate.py:241): one
+    Python pass over every module per token, three launches per delta module.  At decode sizes that host work is
+    several times the GPU time, so here the single-token forward (static KV cache, fixed shapes) is captured once
+    per (batch, cache length) and replayed; the prompt runs as one ordinary forward (factored path up to 128
+    tokens, reconstructed path above).  Output format is ``generate``'s: (batch, prompt + new) token ids.  Stopping
+    criteria are the caller's business: all `max_new_tokens` tokens are produced, unless `eos_token_id` is given, in
+    which case rows that have emitted it are padded with `pad_token_id` from then on (as ``generate`` pads them).
+
+    ``check_status=True`` (default) reads the factored kernel's status words once at the end of every call and
+    raises if a grid-wide wait expired during it.
+    """
+
+    def __init__(self, model, check_status: bool = True):
+        self.model = model
+        self.check_status = check_status
+        self._graphs = {}          # (batch, max_len) -> (graph, cache, tok, pos, next)
+
+    def _step(self, cache, tok, pos):
+        out = self.model(input_ids=tok, past_key_values=cache, cache_position=pos, use_cache=True)
+        return out.logits[:, -1].argmax(-1, keepdim=True)
+
+    def _prefill(self, cache, ids):
+        pos = torch.arange(ids.shape[1], device=ids.device)
+        out = self.model(input_ids=ids, past_key_values=cache, cache_position=pos, use_cache=True)
+        return out.logits[:, -1].argmax(-1, keepdim=True)
+
+    def _captured(self, batch, max_len, device):
+        from transformers import StaticCache
+
+        for (b, ml), entry in self._graphs.items():            # a graph with a longer cache serves shorter requests too
+            if b == batch and ml >= max_len:
+                return entry
+        key = (batch, max_len)
+        if key not in self._graphs:
+            cfg = self.model.config
+            tok = torch.zeros(batch, 1, dtype=torch.long, device=device)
+            pos = torch.zeros(1, dtype=torch.long, device=device)
+            # warm-up on a throw-away cache (lazy initialisation, scratch buffers of the kernels) on a side stream
+            spare = StaticCache(config=cfg, max_cache_len=max_len)
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step(spare, tok, pos)
+            torch.cuda.current_stream().wait_stream(side)
+            del spare
+            cache = StaticCache(config=cfg, max_cache_len=max_len)
+            self._step(cache, tok, pos)                        # allocates the cache's tensors outside the capture
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                nxt = self._step(cache, tok, pos)
+            self._graphs[key] = (graph, cache, tok, pos, nxt)
+        return self._graphs[key]
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens: int, eos_token_id=None, pad_token_id=0, use_graph: bool = True,
+                 timings: dict | None = None):
+        """(batch, prompt) token ids -> (batch, prompt + max_new_tokens).  use_graph=False runs the same loop eagerly
+        (the two produce the same tokens; the eager loop is what a plain ``model.generate`` costs).  When `timings`
+        is a dict it receives ``prefill_ms`` and ``decode_ms`` (CUDA events around the prompt forward and around the
+        max_new_tokens - 1 decode steps; the call then synchronises)."""
+        from transformers import StaticCache
+
+        batch, prompt = input_ids.shape
+        device = input_ids.device
+        max_len = prompt + max_new_tokens + 1
+        if use_graph:
+            graph, cache, tok, pos, nxt = self._captured(batch, max_len, device)
+        else:
+            cache = StaticCache(config=self.model.config, max_cache_len=max_len)
+            tok = torch.zeros(batch, 1, dtype=torch.long, device=device)
+            pos = torch.zeros(1, dtype=torch.long, device=device)
+        cache.reset()
+        out = torch.empty(batch, prompt + max_new_tokens, dtype=torch.long, device=device)
+        out[:, :prompt] = input_ids
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if timings is not None else None
+        if ev:
+            ev[0].record()
+        first = self._prefill(cache, input_ids)
+        if ev:
+            ev[1].record()
+        tok.copy_(first)
+        pos.fill_(prompt)
+        alive = torch.ones(batch, 1, dtype=torch.bool, device=device)
+        for i in range(max_new_tokens):
+            cur = tok.clone()
+            if eos_token_id is not None:
+                cur = torch.where(alive, cur, torch.full_like(cur, pad_token_id))
+                alive = alive & (cur != eos_token_id)
+            out[:, prompt + i] = cur[:, 0]
+            if i + 1 == max_new_tokens:
+                break
+            if use_graph:
+                graph.replay()
+                tok.copy_(nxt)
+            else:
+                tok.copy_(self._step(cache, tok, pos))
+            pos.add_(1)
+        if ev:
+            ev[2].record()
+            torch.cuda.synchronize(device)
+            timings["prefill_ms"], timings["decode_ms"] = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+        if self.check_status:
+            from .kernels import check_factored_status
+
+            check_factored_status(device)
+        return out
+
+
+def greedy_generate(model, input_ids, max_new_tokens: int, **kw):
+    """``model.generate(input_ids, do_sample=False, max_new_tokens=...)`` with the decode step replayed from a CUDA
+    graph; the decoder (and its captured graphs) is cached on the model."""
+    dec = getattr(model, "_ade_graph_decoder", None)
+    if dec is None:
+        dec = model._ade_graph_decoder = GreedyGraphDecoder(model)
+    return dec.generate(input_ids, max_new_tokens, **kw)

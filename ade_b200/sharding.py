@@ -52,22 +52,33 @@ def replica_plan(n_deltas: int, world: int):
     return [[d for d in range(n_deltas) if d % world == r] for r in range(world)]
 
 
-def gather_merged(local: dict, shapes: dict, plan, group=None):
+def gather_merged(local: dict, shapes: dict, plan, group=None, device=None, dtype=torch.bfloat16):
     """Assemble reconstructed weights from all ranks.
 
     local:  {module index: merged tensor} of this rank (the modules plan[rank] lists).
     shapes: {module index: (d_o, d_i)} for every module.
     plan:   output of ``partition_modules``.
-    Returns {module index: tensor} with every module, on the device of the local tensors.  One
-    all_gather per round; ranks that have run out of modules contribute an empty tensor.
+    device: where the exchange buffers live; default: the device of the local tensors, else the current
+            CUDA device when the process group runs over NCCL, else the CPU.  A rank whose plan is empty has no
+            local tensor to take it from, and NCCL needs its (empty-handed) contribution on a GPU as well.
+    dtype:  element type of the shards (all ranks must agree; bfloat16 is what the kernel writes).
+    Returns {module index: tensor} with every module, on `device`.  One all_gather per round; ranks that
+    have run out of modules contribute zeros.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if sorted(local) != plan[rank]:
         raise ValueError(f"rank {rank} holds modules {sorted(local)} but the plan assigns {plan[rank]}")
     some = next(iter(local.values())) if local else None
-    device = some.device if some is not None else torch.device("cpu")
-    dtype = some.dtype if some is not None else torch.bfloat16
+    if device is None:
+        if some is not None:
+            device = some.device
+        elif dist.get_backend(group) == "nccl":
+            device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            device = torch.device("cpu")
+    if some is not None and some.dtype != dtype:
+        raise ValueError(f"local shards are {some.dtype}, the exchange was asked for {dtype}")
     out = dict(local)
     for rnd in range(max(len(p) for p in plan)):
         idx = [p[rnd] if rnd < len(p) else None for p in plan]

@@ -75,12 +75,19 @@ def synthetic_module(d_o, d_i, rank, config=0, module=0, device="cpu", exact_svd
     return W_b, packed
 
 
-def random_packed(d_o, d_i, rank, seed, device="cpu"):
+def random_packed(d_o, d_i, rank, seed, device="cpu", on_device=False):
     """Packed fields drawn directly (uniform codes, log-normal scales, uniform zero-points): same
     shapes, dtypes and value ranges as a compressed module, no SVD.  For size sweeps and
-    multi-hundred-module models."""
-    g = torch.Generator().manual_seed(seed)
+    multi-hundred-module models.  on_device=True draws with the device's own generator (another
+    stream of numbers, same distributions), which is what makes a 224-module model a matter of seconds."""
     ng = rank // 128
+    if on_device:
+        g = torch.Generator(device=device).manual_seed(seed)
+        ri = lambda *shape: torch.randint(0, 16, shape, generator=g, device=device)
+        sc = lambda *shape: (torch.exp(torch.randn(*shape, generator=g, device=device) * 0.3) * 2e-4).to(torch.bfloat16)
+        return {"U_codes": ri(d_o, rank).to(torch.uint8), "U_scale": sc(d_o, ng), "U_zero": ri(d_o, ng).to(torch.bfloat16),
+                "Vt_codes": ri(rank, d_i).to(torch.uint8), "Vt_scale": sc(ng, d_i), "Vt_zero": ri(ng, d_i).to(torch.bfloat16)}
+    g = torch.Generator().manual_seed(seed)
     return {
         "U_codes": torch.randint(0, 16, (d_o, rank), generator=g, dtype=torch.uint8).to(device),
         "U_scale": (torch.exp(torch.randn(d_o, ng, generator=g) * 0.3) * 2e-4).to(torch.bfloat16).to(device),
@@ -105,3 +112,44 @@ def draw_ranks(shapes, alpha=1.0 / 16, seed=0, lo=128, hi=1024):
             break
         ranks[i] -= 128
     return ranks
+
+
+LLAMA_ARCH = {
+    "7b": dict(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32),
+    "13b": dict(hidden_size=5120, intermediate_size=13824, num_hidden_layers=40, num_attention_heads=40),
+    "tiny": dict(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8),
+}
+
+
+def synthetic_llama(arch="7b", layers=None, seed=0, device="cuda", vocab=32000, fuse=True, alpha=1.0 / 16):
+    """Random-init bfloat16 LLaMA-architecture model with a synthetic delta on every linear module, each an
+    ``ADEKernelLinear`` (configs 2-4 of the benchmark; no checkpoint or dataset is involved).  Ranks are drawn for
+    the alpha bit budget (``draw_ranks``), packed fields directly on the device (``random_packed``).  Returns
+    (model, ranks, number of fused q/k/v and gate/up groups)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from .serving import LINEAR_MODULE_NAMES, ADEKernelLinear, fuse_kernel_linears
+
+    kw = dict(LLAMA_ARCH[arch])
+    if layers is not None:
+        kw["num_hidden_layers"] = layers
+    cfg = LlamaConfig(vocab_size=vocab, num_key_value_heads=kw["num_attention_heads"], max_position_embeddings=4096, **kw)
+    torch.manual_seed(seed)
+    with torch.device(device):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    shapes = [tuple(model.model.layers[li].get_submodule(n).weight.shape)
+              for li in range(cfg.num_hidden_layers) for n in LINEAR_MODULE_NAMES]
+    ranks = draw_ranks(shapes, alpha=alpha, seed=seed)
+    i = 0
+    for li in range(cfg.num_hidden_layers):
+        layer = model.model.layers[li]
+        for name in LINEAR_MODULE_NAMES:
+            owner, _, leaf = name.rpartition(".")
+            parent = layer.get_submodule(owner)
+            lin = getattr(parent, leaf)
+            d_o, d_i = lin.weight.shape
+            packed = random_packed(d_o, d_i, ranks[i], 1000 * seed + i, device, on_device=True)
+            setattr(parent, leaf, ADEKernelLinear(lin.weight.data, packed))
+            i += 1
+    groups = fuse_kernel_linears(model) if fuse else 0
+    return model, ranks, groups

@@ -81,8 +81,8 @@ typedef struct ade_delta {
     const uint16_t* vs;
     const uint8_t* vz;
     int M, N, r;
-    /* Optional hint for a block-diagonal U^ (several modules that share their input served as one, see
-     * INTEGRATION.md section 6): rows [block_rows[i], block_rows[i+1]) hold non-zero codes only in the rank
+    /* Optional hint for a block-diagonal U^ (several modules that share their input served as one launch:
+     * d_o and rank are the members' sums, V^T is stacked along the rank axis): rows [block_rows[i], block_rows[i+1]) hold non-zero codes only in the rank
      * groups [block_groups[i], block_groups[i+1]), i < n_blocks <= ADE_B200_MAX_BLOCKS, and (code - zero) is
      * exactly 0 elsewhere.  The factored kernel then skips the other groups of those rows.  n_blocks = 0: dense.
      * No counterpart in the reference. */
@@ -135,6 +135,11 @@ int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, 
  * Requirements: 1 <= T <= 128, M >= 1 (at most 320 rows per SM), N % 128 == 0, r % 128 == 0.
  * One kernel is launched on `stream` (one CTA per SM; for T <= 16 four extra warps per CTA compute
  * h while the others already stream w_b); the call does not synchronise.
+ *   The CTAs of that kernel wait for one another, so the launch is cooperative: the grid starts only when
+ *   every SM can take its CTA (work of other streams that holds SMs delays the start instead of starving the
+ *   wait), and a device that cannot hold the grid at all makes the call return ADE_ERR_CUDA.  Should the wait
+ *   for h expire all the same, status word 2 says so: read it (cudaMemcpy of 4 bytes at sync offset + 8)
+ *   wherever a wrong result must not go unnoticed.
  */
 size_t ade_b200_factored_scratch_bytes(int T, int r);
 size_t ade_b200_factored_sync_offset(int T, int r);
@@ -151,18 +156,29 @@ int ade_b200_factored(const ade_delta_t* d, const void* x, const void* y_dense, 
  * runs inside another framework's memory plan, under a fixed memory budget, or in a context where
  * cudaMalloc's implicit device synchronisation is not acceptable.  The entry point calls no cudaMalloc,
  * cudaFree or allocating library routine.
- *   Limit: ade_b200_factored_scratch_bytes(T, r) <= ADE_B200_STATIC_SCRATCH_BYTES, i.e. T * r <= 131072 for
- *   T > 16 (e.g. T = 128 at r = 1024) and every supported rank for T <= 16; beyond it ADE_ERR_SCRATCH.
+ *   Limit: 256 + T * r * (T <= 16 ? 8 : 2) <= ADE_B200_STATIC_SCRATCH_BYTES, i.e. T * r <= 131072 above 16
+ *   tokens (T = 128 at r = 1024) and every supported rank up to 16 tokens; beyond it ADE_ERR_SCRATCH.
+ *   Above 16 tokens ade_b200_factored slices the computation of h over d_i when its scratch has room for
+ *   the float32 partial sums; here the slices are as many as fit behind h in the array, possibly fewer,
+ *   possibly one (T = 128 at r = 512 runs unsliced).  With fewer slices the call is slower (about 1.5x at
+ *   T = 128) and h is summed in another order, so the output can differ from ade_b200_factored's in the last
+ *   bit; with the same number of slices the two outputs are identical.
  *   The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
  *   current); make that first call outside any stream capture.
  *   All calls on a device share the one array, and it keeps the previous call's contents; every call
  *   clears the sync words on `stream` before its launch.  Two calls that overlap on the GPU (different
  *   streams without ordering) race on h and on the sync words: serialise them, or use ade_b200_factored
  *   with one buffer per stream.
+ *   The status word (1 = a wait for h expired in some call, output of that call undefined) is kept in the
+ *   array too and survives later calls; ade_b200_factored_static_status copies it out.
  */
 #define ADE_B200_STATIC_SCRATCH_BYTES 262400
 int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_dense, const void* w_b,
                              void* out, int T, void* stream);
+/* Copies the status word of the current device's built-in scratch array to *dst (host or device memory; one
+ * 4-byte cudaMemcpyAsync on `stream`, ordered after the calls issued on it) and, when clear != 0, zeroes the
+ * word afterwards.  Allocates nothing.  No counterpart in the reference. */
+int ade_b200_factored_static_status(int* dst, int clear, void* stream);
 
 /*
  * Reconstructed application (replaces ade_recon_int4, src/kernels.py:383-397):
@@ -183,6 +199,25 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
  */
 int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
                    int32_t* dbg_acc, int* status_dev, void* stream);
+
+/*
+ * Process-wide options.  No counterpart in the reference.
+ *   ADE_OPT_WAIT_LIMIT_CYCLES   clock cycles a wait inside a kernel (for h, for an operand stage, ...) may take
+ *                               before the kernel gives up, records its status and runs to its end; 0 restores the
+ *                               default of about one second.
+ *   ADE_OPT_COOPERATIVE_LAUNCH  1 (default): the factored kernel is launched cooperatively; 0: plain launch, for
+ *                               callers that guarantee an otherwise idle device themselves.
+ *   ADE_OPT_DROP_SIGNALS        diagnostic, default 0.  With 1 the producers inside the kernels stay silent (the
+ *                               phase-A units of the factored kernel do not report, the reconstruction kernels
+ *                               issue no code loads), so every wait that depends on them runs into the limit
+ *                               above: the way to exercise the time-out path without any fault.  Outputs of
+ *                               such calls are undefined.
+ * Returns ADE_OK, or ADE_ERR_SHAPE for an unknown option or a negative limit.
+ */
+#define ADE_OPT_WAIT_LIMIT_CYCLES 1
+#define ADE_OPT_COOPERATIVE_LAUNCH 2
+#define ADE_OPT_DROP_SIGNALS 3
+int ade_b200_set_option(int option, long long value);
 
 #ifdef __cplusplus
 }

@@ -122,6 +122,7 @@ def _check_factored(case, fused):
         y_dense = torch.nn.functional.linear(x, W)
         y = kernels.decode_forward_packed(x, y_dense, p4)
     torch.cuda.synchronize()
+    kernels.check_factored_status(DEV)                     # no grid-wide wait expired in any launch so far
     err, cos = O.parity(y.float().cpu().numpy(), ref)
     assert err <= TOL_ERR and cos >= TOL_COS, (err, cos)
     return y

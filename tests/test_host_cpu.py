@@ -110,6 +110,39 @@ def test_library_exports_every_declared_symbol():
     assert lib.ade_b200_factored_scratch_bytes(0, 256) == 0
 
 
+def test_status_tables_follow_the_header():
+    """The Python tables of return codes and device status codes name exactly what the header defines."""
+    header = open(os.path.join(ROOT, "include", "ade_b200.h")).read()
+    dev = {int(v): k for k, v in re.findall(r"#define (ADE_DEV_TIMEOUT_\w+) (\d+)", header)}
+    assert set(dev) == set(_lib.DEVICE_STATUS) and all(_lib.DEVICE_STATUS[c].startswith(n + ":") for c, n in dev.items())
+    err = {int(v): k for k, v in re.findall(r"#define (ADE_ERR_\w+) \((-\d+)\)", header)}
+    assert set(err) == set(_lib.ERRORS) and all(_lib.ERRORS[c].startswith(n + ":") for c, n in err.items())
+    opts = dict(re.findall(r"#define (ADE_OPT_\w+) (\d+)", header))
+    assert (int(opts["ADE_OPT_WAIT_LIMIT_CYCLES"]), int(opts["ADE_OPT_COOPERATIVE_LAUNCH"]), int(opts["ADE_OPT_DROP_SIGNALS"])) == (
+        _lib.OPT_WAIT_LIMIT_CYCLES, _lib.OPT_COOPERATIVE_LAUNCH, _lib.OPT_DROP_SIGNALS)
+    lib = _lib.load()
+    assert lib.ade_b200_set_option(99, 1) == -2 and lib.ade_b200_set_option(_lib.OPT_WAIT_LIMIT_CYCLES, -5) == -2
+    assert lib.ade_b200_set_option(_lib.OPT_WAIT_LIMIT_CYCLES, 0) == 0          # back to the default
+
+
+def test_packed_file_is_validated_and_mapped(tmp_path):
+    """The reader checks every module's shapes against each other, the writer refuses inconsistent modules and leaves
+    no partial file behind."""
+    good = synth.random_packed(128, 256, 256, seed=6)
+    path = str(tmp_path / "d.pt")
+    packed_io.save_packed(path, {"model.layers.0.mlp.gate_proj": good}, {"bits": 4, "group_size": 128})
+    f = packed_io.PackedDeltaFile(path)
+    assert len(f) == 1 and "model.layers.0.mlp.gate_proj" in f and f.dims["model.layers.0.mlp.gate_proj"] == (128, 256, 256)
+    assert torch.equal(f.module("model.layers.0.mlp.gate_proj")["Vt_codes"], good["Vt_codes"])
+    bad = dict(good, U_scale=good["U_scale"][:, :1])
+    with pytest.raises(ValueError):
+        packed_io.save_packed(str(tmp_path / "bad.pt"), {"m": bad}, {})
+    assert sorted(os.listdir(tmp_path)) == ["d.pt"]
+    torch.save({"__meta__": {"format": "ade_packed_v1"}, **{f"m.{k}": v for k, v in bad.items()}}, path)
+    with pytest.raises(ValueError):
+        packed_io.PackedDeltaFile(path)
+
+
 def test_argument_errors_before_any_launch():
     """Bad arguments are rejected by status code before anything touches a device."""
     lib = _lib.load()

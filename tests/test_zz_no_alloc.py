@@ -18,6 +18,14 @@ from ade_b200 import _lib, kernels, synth
 pytestmark = pytest.mark.gpu
 
 
+def _static_status(lib, stream, clear=0):
+    """The sticky status word of the built-in array, fetched into a device int by the accessor."""
+    word = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    assert lib.ade_b200_factored_static_status(word.data_ptr(), clear, stream) == 0
+    torch.cuda.synchronize()
+    return int(word.item())
+
+
 def test_static_scratch_entry_matches_the_regular_one():
     dev = "cuda"
     lib = _lib.load()
@@ -35,6 +43,7 @@ def test_static_scratch_entry_matches_the_regular_one():
             assert rc == 0, _lib.ERRORS.get(rc, rc)
             torch.cuda.synchronize()
             assert torch.equal(out, ref)
+            assert _static_status(lib, stream) == 0                            # no wait for h expired
         # the reference's calling convention (y_dense supplied) through the same entry
         yd = torch.nn.functional.linear(x, W)
         ref2 = kernels.decode_forward_packed(x, yd, p4)
@@ -42,6 +51,23 @@ def test_static_scratch_entry_matches_the_regular_one():
         assert lib.ade_b200_factored_static(ctypes.byref(d), x.data_ptr(), yd.data_ptr(), None, out2.data_ptr(), T, stream) == 0
         torch.cuda.synchronize()
         assert torch.equal(out2, ref2)
+    # T = 128 at r = 512: h fills the array, no room is left for partial sums, so this entry computes h unsliced while
+    # the regular entry (with its recommended scratch) slices it four ways.  Other summation order: compared with
+    # the oracle's tolerance against the regular entry instead of bit for bit.
+    from oracle import oracle as O
+    M, N, r, T = 384, 4096, 512, 128
+    p4 = kernels.pack_int4(synth.random_packed(M, N, r, seed=77), device=dev)
+    W = synth.base_weight(M, N, 13).to(dev)
+    x = synth.activations(T, N, 14).to(dev)
+    yd = torch.nn.functional.linear(x, W)
+    ref3 = kernels.decode_forward_packed(x, yd, p4)
+    out3 = torch.empty_like(ref3)
+    assert lib.ade_b200_factored_static(ctypes.byref(kernels._cdelta(p4)), x.data_ptr(), yd.data_ptr(), None,
+                                        out3.data_ptr(), T, stream) == 0
+    torch.cuda.synchronize()
+    err, cos = O.parity(out3.float().cpu().numpy(), ref3.float().cpu().numpy())
+    assert err <= 1e-2 and cos >= 0.9999, (err, cos)
+    assert _static_status(lib, stream, clear=1) == 0
     # T * r beyond the built-in buffer is refused before any launch
     p4 = kernels.pack_int4(synth.random_packed(128, 128, 2048, seed=3), device=dev)
     x = synth.activations(128, 128, 4).to(dev)
