@@ -40,7 +40,7 @@ OPT_WAIT_LIMIT_CYCLES, OPT_COOPERATIVE_LAUNCH, OPT_DROP_SIGNALS = 1, 2, 3
 # every symbol include/ade_b200.h declares
 EXPORTS = (
     "ade_b200_device_status", "ade_b200_version", "ade_b200_last_cuda_error",
-    "ade_b200_pack_codes", "ade_b200_pack_zeros",
+    "ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_compress_rows",
     "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored",
     "ade_b200_factored_static", "ade_b200_factored_static_status", "ade_b200_recon", "ade_b200_set_option",
 )
@@ -82,6 +82,8 @@ def load() -> ctypes.CDLL:
     lib.ade_b200_last_cuda_error.restype = ci
     lib.ade_b200_pack_codes.argtypes = [vp, vp, ci, ci, ci, vp]
     lib.ade_b200_pack_zeros.argtypes = [vp, vp, sz, vp]
+    lib.ade_b200_compress_rows.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.ade_b200_compress_rows.restype = ci
     lib.ade_b200_factored_scratch_bytes.argtypes = [ci, ci]
     lib.ade_b200_factored_scratch_bytes.restype = sz
     lib.ade_b200_factored_sync_offset.argtypes = [ci, ci]

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "compress.cuh"
 #include "factored.cuh"
 #include "recon.cuh"
 #include "recon_strip.cuh"
@@ -37,6 +38,9 @@ DeviceInfo g_dev[kMaxDevices];
 long long g_wait_limit = ade::RC_SPIN_LIMIT;   // clock cycles a device-side wait may take before it gives up
 int g_cooperative = 1;                         // factored kernel launched cooperatively (co-residency guaranteed)
 int g_drop_signals = 0;                        // diagnostic: producers inside the kernels stay silent
+#ifdef ADE_TRACE
+unsigned long long* g_trace = nullptr;         // development builds: device buffer for event stamps (option 100)
+#endif
 
 template <int NT>
 bool optin_factored();
@@ -61,6 +65,9 @@ int device_info(const DeviceInfo** out) {
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                return ADE_ERR_CUDA;
+            if (!cuda_ok(cudaFuncSetAttribute(ade::compress_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              static_cast<int>(ade::compress_smem_bytes(ade::CQ_MAX_RANK, true)))))
                 return ADE_ERR_CUDA;
             if (!optin_factored<1>() || !optin_factored<2>() || !optin_factored<4>() || !optin_factored<8>() ||
                 !optin_factored<16>())
@@ -437,6 +444,26 @@ int ade_b200_factored_static(const ade_delta_t* d, const void* x, const void* y_
     return launch_factored<16>(p, grid, st);
 }
 
+int ade_b200_compress_rows(const float* x, const float* sqrt_s, uint8_t* codes, uint16_t* scale, uint16_t* zero, int rows,
+                           int r, int rotate, int transposed, void* stream) {
+    if (!x || !codes || !scale || !zero) return ADE_ERR_NULL;
+    if (rows < 1 || r < ADE_B200_GROUP || r > ade::CQ_MAX_RANK || r % ADE_B200_GROUP) return ADE_ERR_SHAPE;
+    if (rotate && (r & (r - 1))) return ADE_ERR_SHAPE;                  // the in-kernel rotation is the Hadamard transform
+    if (transposed && !aligned16(codes)) return ADE_ERR_ALIGN;
+    const DeviceInfo* di = nullptr;
+    const int rc = device_info(&di);
+    if (rc) return rc;
+    const int blocks_wanted = (rows + ade::CQ_ROWS - 1) / ade::CQ_ROWS;
+    const int grid = blocks_wanted < 8 * di->sms ? blocks_wanted : 8 * di->sms;
+    const size_t smem = ade::compress_smem_bytes(r, transposed != 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    __nv_bfloat16* sc = reinterpret_cast<__nv_bfloat16*>(scale);
+    __nv_bfloat16* zp = reinterpret_cast<__nv_bfloat16*>(zero);
+    if (transposed) ade::compress_rows_kernel<true><<<grid, ade::CQ_THREADS, smem, st>>>(x, sqrt_s, codes, sc, zp, rows, r, rotate);
+    else ade::compress_rows_kernel<false><<<grid, ade::CQ_THREADS, smem, st>>>(x, sqrt_s, codes, sc, zp, rows, r, rotate);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
 int ade_b200_factored_static_status(int* dst, int clear, void* stream) {
     if (!dst) return ADE_ERR_NULL;
     char* base = nullptr;
@@ -460,6 +487,11 @@ int ade_b200_set_option(int option, long long value) {
         case ADE_OPT_DROP_SIGNALS:
             g_drop_signals = value != 0;
             return ADE_OK;
+#ifdef ADE_TRACE
+        case 100:
+            g_trace = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value));
+            return ADE_OK;
+#endif
         default:
             return ADE_ERR_SHAPE;
     }
@@ -493,6 +525,10 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     p.one = 1.0f;
     p.spin_limit = g_wait_limit;
     p.drop_loads = g_drop_signals;
+    p.trace = nullptr;
+#ifdef ADE_TRACE
+    p.trace = g_trace;
+#endif
     const int ng = d->r / ADE_B200_GROUP;
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;

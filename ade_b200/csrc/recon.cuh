@@ -65,7 +65,20 @@ struct ReconParams {
     float one;      // 1.0f, set by the host: a value the assembler cannot fold (see recon_strip.cuh)
     long long spin_limit;   // clock cycles after which a wait gives up (RC_SPIN_LIMIT unless the host lowered it)
     int drop_loads;         // diagnostic: the code loads are not issued, so that the waits for them run out
+    unsigned long long* trace;   // development builds (ADE_TRACE) only: event stamps of CTA 0, else nullptr
 };
+
+// Development aid, compiled out unless ADE_TRACE is defined: CTA 0 appends (code << 48 | clock) to one of a few
+// tracks of 4096 stamps each; the host turns them into a timeline of the roles.
+#ifdef ADE_TRACE
+#define ADE_TRACE_STAMP(p, cnt, track, code)                                                                         \
+    do {                                                                                                              \
+        if ((p).trace && blockIdx.x == 0 && (cnt) < 4096)                                                             \
+            (p).trace[(track) * 4096 + (cnt)++] = (static_cast<unsigned long long>(code) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
+    } while (0)
+#else
+#define ADE_TRACE_STAMP(p, cnt, track, code) do { } while (0)
+#endif
 
 // what a bounded wait needs to give up: the CTA's abort flag, the caller's status word, the cycle limit
 struct WaitCtx {

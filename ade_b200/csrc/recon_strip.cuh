@@ -183,20 +183,40 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 
         uint32_t it = 0;
         int j = 0;
+#ifdef ADE_TRACE
+        int tcn = 0;
+        const int ttrack = warp == 0 ? 0 : 1;
+        const bool tr = (warp == 0 || warp == 9) && lane == 0;
+#define EPI_STAMP(code) do { if (tr) ADE_TRACE_STAMP(p, tcn, ttrack, code); } while (0)
+#else
+#define EPI_STAMP(code) do { } while (0)
+#endif
         for (int tile = t_begin; tile < t_end; ++tile, ++j) {
             const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
             const int m = m0 + row;
+            EPI_STAMP(0x0100 | (j & 255));
             const bool live = m < p.M;
             const uint32_t b = j & 1, jph = (j >> 1) & 1;
             const uint32_t wbb = C::WB_BUFS == 2 ? b : 0, wph = C::WB_BUFS == 2 ? jph : static_cast<uint32_t>(j & 1);
             const uint32_t box = box0 + wbb * RS_BOX_BYTES;
             const uint32_t wbar = bar(C::BAR_WB + C::WB_BUFS * warp + wbb);
+#ifdef RS_WB_AHEAD
+            // two box buffers: the base box of tile j + 1 is requested during tile j (after its first group, when the
+            // store of tile j - 1 has long finished reading that buffer), so it has a whole tile to arrive
+            if (C::WB_BUFS == 2) {
+                if (lane == 0 && j == 0) {
+                    mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
+                    tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
+                }
+            } else
+#endif
             if (lane == 0) {
                 bulk_wait_group_read<C::WB_BUFS - 1>();  // the store that last read this box buffer is done with it
                 mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
                 tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
             }
             wait_bounded(bar(C::BAR_SC_FULL + b), jph, wctx, 5);
+            EPI_STAMP(0x0200 | (j & 255));
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);          // this tile's tables
 
             uint64_t acc[16];
@@ -207,6 +227,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                 wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
+                EPI_STAMP(0x0300 | g);
                 tc_fence_after();
                 const uint32_t scg = sct + g * RS_SC_BYTES;
                 const float u = __uint_as_float(lds4(scg + row * 4));
@@ -223,6 +244,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
                     tmem_ld16(tbase + ch * 16, vc);
                     tmem_ld_wait();
+                    EPI_STAMP(0x0400 | (g << 1) | ch);
                     tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
 #pragma unroll
                     for (int h4 = 0; h4 < 2; ++h4) {
@@ -244,14 +266,28 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                                                                         vc[i + 3] - RC_MAGIC);
                     }
                 }
+                EPI_STAMP(0x0500 | g);
                 tmem_st_wait();                          // accumulator stage re-armed: hand it back
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(C::BAR_TEMPTY + a));
+                EPI_STAMP(0x0600 | g);
+#ifdef RS_WB_AHEAD
+                if (C::WB_BUFS == 2 && g == 0 && lane == 0 && tile + 1 < t_end) {
+                    const int tn = tile + 1;
+                    const uint32_t nb = (j + 1) & 1;
+                    const uint32_t nbar = bar(C::BAR_WB + C::WB_BUFS * warp + nb);
+                    bulk_wait_group_read<0>();
+                    mbar_arrive_expect_tx(nbar, RS_BOX_BYTES);
+                    tma_load_2d(box0 + nb * RS_BOX_BYTES, &maps.wb, ((tn % tiles_n) << 7) + hh * 32, ((tn / tiles_n) << 7) + q * 32, nbar);
+                }
+#endif
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::BAR_SC_EMPTY + b));             // this warp is done with the scale tables
+            EPI_STAMP(0x0700 | (j & 255));
             wait_bounded(wbar, wph, wctx, 6);
+            EPI_STAMP(0x0800 | (j & 255));
             uint4 wv4[4];                                // 8 columns per 16-byte chunk
 #pragma unroll
             for (int c = 0; c < 4; ++c) wv4[c] = lds16(box + own + ((c ^ swz) << 4));
@@ -275,6 +311,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 tma_store_2d(&maps.out, n0 + hh * 32, m0 + q * 32, box);
                 bulk_commit_group();
             }
+            EPI_STAMP(0x0900 | (j & 255));
         }
         if (lane == 0) bulk_wait_group_read<0>();    // shared memory may go once the last store has read it
     } else if (warp < RS_MMA_WARP) {
@@ -283,6 +320,12 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         const int c = pt & 3, rbase = pt >> 2;
         uint32_t ri = 0, bi = 0, sk = 0;
         int cur_strip = -1;
+#ifdef ADE_TRACE
+        int tcn = 0;
+#define UNP_STAMP(code) do { if (pt == 0) ADE_TRACE_STAMP(p, tcn, 2, code); } while (0)
+#else
+#define UNP_STAMP(code) do { } while (0)
+#endif
         uint64_t za_pack[4] = {0, 0, 0, 0};               // zero-points of this thread's four U rows, one byte per group
         for (int tile = t_begin; tile < t_end; ++tile) {
             const int strip = tile / tiles_n;
@@ -318,7 +361,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
             for (int g = 0; g < ng; ++g, ++ri, ++bi) {
                 const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
+                UNP_STAMP(0x1000 | g);
                 wait_bounded(bar(C::BAR_RAW_FULL + slot), ph, wctx, 8);
+                UNP_STAMP(0x1100 | g);
                 const uint32_t rs = rawr + slot * RS_RAW_SLOT;
                 uint4 qb[4];
                 uint32_t zb[4];
@@ -331,25 +376,33 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 if (lane == 0) mbar_arrive(bar(C::BAR_RAW_EMPTY + slot));
                 const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
                 wait_bounded(bar(C::BAR_B_EMPTY + s), bph ^ 1, wctx, 2);
+                UNP_STAMP(0x1200 | g);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) unpack_store_s(b_st + s * RS_OPER_BYTES, rbase + 32 * i, c, qb[i], zb[i]);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(C::BAR_B_FULL + s));
+                UNP_STAMP(0x1300 | g);
             }
         }
     } else if (warp == RS_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t it = 0, bi = 0, k = 0;
+#ifdef ADE_TRACE
+            int tcn = 0;
+#endif
             for (int tile = t_begin; tile < t_end; ++tile) {
                 const bool first = tile == t_begin || tile % tiles_n == 0;
                 const bool last = tile == t_end - 1 || (tile + 1) % tiles_n == 0;
                 for (int g = 0; g < ng; ++g, ++it, ++bi) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                     const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
+                    ADE_TRACE_STAMP(p, tcn, 3, 0x2000 | g);
                     wait_bounded(bar(C::BAR_TEMPTY + a), aph, wctx, 4);
+                    ADE_TRACE_STAMP(p, tcn, 3, 0x2100 | g);
                     wait_bounded(bar(C::BAR_B_FULL + s), bph, wctx, 1);
+                    ADE_TRACE_STAMP(p, tcn, 3, 0x2200 | g);
                     if (first) wait_bounded(bar(C::BAR_A_FULL + g), k & 1, wctx, 9);
                     tc_fence_after();
                     const uint64_t ad = smem_desc_k_sw128(a_res + g * RS_OPER_BYTES);
@@ -360,6 +413,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     tc_commit(bar(C::BAR_B_EMPTY + s));
                     tc_commit(bar(C::BAR_TFULL + a));
                     if (last && g == ng - 1) tc_commit(bar(C::BAR_A_FREE));    // the strip of U may be overwritten
+                    ADE_TRACE_STAMP(p, tcn, 3, 0x2300 | g);
                 }
                 if (last) ++k;
             }
@@ -372,6 +426,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             prefetch_tensormap(&maps.vq);
             uint32_t ri = 0;
             int cur_strip = -1;
+#ifdef ADE_TRACE
+            int tcn = 0;
+#endif
             for (int tile = t_begin; tile < t_end; ++tile) {
                 const int strip = tile / tiles_n, n0 = (tile % tiles_n) << 7;
                 if (strip != cur_strip) {
@@ -386,6 +443,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 for (int g = 0; g < ng; ++g, ++ri) {
                     const uint32_t slot = ri % C::RAW_DEPTH, ph = (ri / C::RAW_DEPTH) & 1;
                     wait_bounded(bar(C::BAR_RAW_EMPTY + slot), ph ^ 1, wctx, 10);
+                    ADE_TRACE_STAMP(p, tcn, 4, 0x3000 | g);
                     mbar_arrive_expect_tx(bar(C::BAR_RAW_FULL + slot), RS_RAW_CODES + 128);
                     tma_load_2d(rawr + slot * RS_RAW_SLOT, &maps.vq, g * 64, n0, bar(C::BAR_RAW_FULL + slot));
                     bulk_g2s(rawr + slot * RS_RAW_SLOT + RS_RAW_CODES, p.vz + static_cast<size_t>(g) * p.N + n0, 128,

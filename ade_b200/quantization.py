@@ -88,6 +88,9 @@ def compress_module(U, S, V, bits: int = 4, group_size: int = 128, generator=Non
     U (d_o, r), S (r,), V (d_i, r) on any device.  Returns the packed dict (CPU tensors unless
     `keep_device`).  `generator` (CPU) is consumed only for non-power-of-two ranks.
     """
+    if U.is_cuda and bits == 4 and group_size == 128 and S.shape[0] % 128 == 0 and S.shape[0] <= 2048:
+        out = compress_module_cuda(U, S, V, generator)
+        return out if keep_device else {k: v.cpu() for k, v in out.items()}
     U = U.float()
     S = S.float().clamp(min=1e-8)
     Vt = V.transpose(-1, -2).contiguous().float()
@@ -100,6 +103,52 @@ def compress_module(U, S, V, bits: int = 4, group_size: int = 128, generator=Non
     Vc, Vs, Vz = quantize_colwise(H.T @ (root.unsqueeze(1) * Vt), bits, group_size)
     out = {"U_codes": Uc, "U_scale": Us, "U_zero": Uz, "Vt_codes": Vc, "Vt_scale": Vs, "Vt_zero": Vz}
     return out if keep_device else {k: v.cpu() for k, v in out.items()}
+
+
+def compress_module_cuda(U, S, V, generator=None) -> dict:
+    """compress_module on the GPU through ``ade_b200_compress_rows``: per factor one kernel that scales by sqrt(S),
+    rotates (fast Walsh-Hadamard transform for a power-of-two rank; for other ranks the seeded random orthogonal H is
+    applied here with one dense matmul, as the reference does) and quantises the groups in shared memory.  4 bits,
+    groups of 128.  Returns the packed dict on the device of U."""
+    from . import _lib
+
+    lib = _lib.load()
+    dev = U.device
+    rank = int(S.shape[0])
+    root = torch.sqrt(S.to(dev, torch.float32).clamp(min=1e-8)).contiguous()
+    Uf = U.to(torch.float32).contiguous()
+    Vf = V.to(dev, torch.float32).contiguous()                         # (d_i, r): the V side is quantised row by row too
+    pow2 = rank & (rank - 1) == 0
+    if not pow2:
+        H = rotation_matrix(rank, generator=generator).to(dev)
+        Uf = (Uf * root.unsqueeze(0)) @ H
+        Vf = (Vf * root.unsqueeze(0)) @ H                              # ((V sqrt(S)) H)^T = H^T (sqrt(S) V^T)
+    d_o, d_i, ng = Uf.shape[0], Vf.shape[0], rank // 128
+    out = {"U_codes": torch.empty(d_o, rank, dtype=torch.uint8, device=dev),
+           "U_scale": torch.empty(d_o, ng, dtype=torch.bfloat16, device=dev),
+           "U_zero": torch.empty(d_o, ng, dtype=torch.bfloat16, device=dev),
+           "Vt_codes": torch.empty(rank, d_i, dtype=torch.uint8, device=dev),
+           "Vt_scale": torch.empty(ng, d_i, dtype=torch.bfloat16, device=dev),
+           "Vt_zero": torch.empty(ng, d_i, dtype=torch.bfloat16, device=dev)}
+    with torch.cuda.device(dev):
+        st = torch.cuda.current_stream().cuda_stream
+        sp = root.data_ptr() if pow2 else None
+        _lib.check(lib.ade_b200_compress_rows(Uf.data_ptr(), sp, out["U_codes"].data_ptr(), out["U_scale"].data_ptr(),
+                                              out["U_zero"].data_ptr(), d_o, rank, int(pow2), 0, st), "ade_b200_compress_rows(U)")
+        _lib.check(lib.ade_b200_compress_rows(Vf.data_ptr(), sp, out["Vt_codes"].data_ptr(), out["Vt_scale"].data_ptr(),
+                                              out["Vt_zero"].data_ptr(), d_i, rank, int(pow2), 1, st), "ade_b200_compress_rows(V)")
+    return out
+
+
+def fold_scales(packed: dict, gamma: torch.Tensor, rho: torch.Tensor) -> dict:
+    """Fold the tuning vectors of the reference's fold-in stage into the per-group scales, u <- gamma u (per output
+    row), v <- rho v (per input column): what ``FoldInLinear.export_folded`` writes (src/adaptation.py:244-263).  The
+    codes and zero-points are shared with `packed`; the scales are new bfloat16 tensors."""
+    us, vs = packed["U_scale"], packed["Vt_scale"]
+    out = dict(packed)
+    out["U_scale"] = (us.float() * gamma.to(us.device).float().unsqueeze(1)).to(us.dtype)
+    out["Vt_scale"] = (vs.float() * rho.to(vs.device).float().unsqueeze(0)).to(vs.dtype)
+    return out
 
 
 def group_cost_bits(d_o: int, d_i: int, b_quant: int = 4, b_s: int = 16, b_z: int | None = None,

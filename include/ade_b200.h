@@ -110,6 +110,23 @@ int ade_b200_pack_codes(const uint8_t* codes, uint8_t* out, int rows, int K, int
 int ade_b200_pack_zeros(const uint16_t* zeros_bf16, uint8_t* out, size_t count, void* stream);
 
 /*
+ * Producer side of the format on the device: one factor of a truncated SVD to codes, scales and zero-points in one
+ * pass (replaces, per factor, the chain of src/quantization.py:244-285: scaling by sqrt(S) :266-268, the shared
+ * rotation H :270-272, and quantize_rowwise / quantize_colwise :134-199 with _pin_zero_in_range :109-131).
+ *   x        float32 [rows][r]: U (d_o, r), or V (d_i, r) with its singular vectors as columns.
+ *   sqrt_s   float32 [r] multiplied into every row first, or NULL.
+ *   rotate   != 0: apply the normalised Sylvester Hadamard rotation of order r (a power of two) inside the kernel,
+ *            as a fast Walsh-Hadamard transform; 0: x is quantised as it is (the caller applied another rotation,
+ *            e.g. the seeded random orthogonal matrix the reference uses for other ranks).
+ *   transposed == 0: codes uint8 [rows][r] (one 4-bit code per byte), scale / zero bf16 [rows][r/128]: the U side.
+ *   transposed != 0: codes [r][rows], scale / zero [r/128][rows]: the V side, H^T (sqrt(S) V^T) = ((V sqrt(S)) H)^T.
+ * The quantisation is the reference's float32 arithmetic operation for operation: with rotate == 0 the outputs are
+ * bit-identical to quantize_rowwise / quantize_colwise on the same input.  r % 128 == 0, r <= 2048.
+ */
+int ade_b200_compress_rows(const float* x, const float* sqrt_s, uint8_t* codes, uint16_t* scale, uint16_t* zero,
+                           int rows, int r, int rotate, int transposed, void* stream);
+
+/*
  * Factored application, T <= 128 tokens (replaces run_ab, src/kernels.py:946-954, and the
  * F.linear that precedes it in src/serving.py:106):
  *
