@@ -155,6 +155,9 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
     const int t_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
     const int t_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
     const WaitCtx wctx{abort_flag, p.status, p.spin_limit};
+    // first tile of this CTA as (strip, n-tile); every role then walks the tiles by incrementing (an integer division
+    // per tile and role is a few hundred cycles of dependent instructions)
+    const int strip0 = t_begin / tiles_n, nt0 = t_begin - strip0 * tiles_n;
 
     if (warp < RS_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
@@ -182,7 +185,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         }
 
         uint32_t it = 0;
-        int j = 0;
+        int j = 0, sm = strip0, nt = nt0;
 #ifdef ADE_TRACE
         int tcn = 0;
         const int ttrack = warp == 0 ? 0 : 1;
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 #define EPI_STAMP(code) do { } while (0)
 #endif
         for (int tile = t_begin; tile < t_end; ++tile, ++j) {
-            const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
+            const int m0 = sm << 7, n0 = nt << 7;
             const int m = m0 + row;
             EPI_STAMP(0x0100 | (j & 255));
             const bool live = m < p.M;
@@ -200,18 +203,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             const uint32_t wbb = C::WB_BUFS == 2 ? b : 0, wph = C::WB_BUFS == 2 ? jph : static_cast<uint32_t>(j & 1);
             const uint32_t box = box0 + wbb * RS_BOX_BYTES;
             const uint32_t wbar = bar(C::BAR_WB + C::WB_BUFS * warp + wbb);
-#ifdef RS_WB_AHEAD
-            // two box buffers: the base box of tile j + 1 is requested during tile j (after its first group, when the
-            // store of tile j - 1 has long finished reading that buffer), so it has a whole tile to arrive
-            if (C::WB_BUFS == 2) {
-                if (lane == 0 && j == 0) {
-                    mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
-                    tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
-                }
-            } else
-#endif
-            if (lane == 0) {
-                bulk_wait_group_read<C::WB_BUFS - 1>();  // the store that last read this box buffer is done with it
+            // base box: with two buffers the box of tile j + 1 is requested during tile j (below), so only the CTA's first
+            // tile asks here; with one buffer every tile asks for its own once the previous store has read the buffer
+            if (lane == 0 && (C::WB_BUFS == 1 || j == 0)) {
+                if (C::WB_BUFS == 1) bulk_wait_group_read<0>();
                 mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
                 tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
             }
@@ -272,16 +267,15 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(C::BAR_TEMPTY + a));
                 EPI_STAMP(0x0600 | g);
-#ifdef RS_WB_AHEAD
                 if (C::WB_BUFS == 2 && g == 0 && lane == 0 && tile + 1 < t_end) {
-                    const int tn = tile + 1;
-                    const uint32_t nb = (j + 1) & 1;
+                    // base box of the next tile into the other buffer; the store that last read it was issued a tile ago
+                    const bool wrap = nt + 1 == tiles_n;
+                    const uint32_t nb = b ^ 1;
                     const uint32_t nbar = bar(C::BAR_WB + C::WB_BUFS * warp + nb);
                     bulk_wait_group_read<0>();
                     mbar_arrive_expect_tx(nbar, RS_BOX_BYTES);
-                    tma_load_2d(box0 + nb * RS_BOX_BYTES, &maps.wb, ((tn % tiles_n) << 7) + hh * 32, ((tn / tiles_n) << 7) + q * 32, nbar);
+                    tma_load_2d(box0 + nb * RS_BOX_BYTES, &maps.wb, ((wrap ? 0 : nt + 1) << 7) + hh * 32, ((wrap ? sm + 1 : sm) << 7) + q * 32, nbar);
                 }
-#endif
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::BAR_SC_EMPTY + b));             // this warp is done with the scale tables
@@ -312,6 +306,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 bulk_commit_group();
             }
             EPI_STAMP(0x0900 | (j & 255));
+            if (++nt == tiles_n) {
+                nt = 0;
+                ++sm;
+            }
         }
         if (lane == 0) bulk_wait_group_read<0>();    // shared memory may go once the last store has read it
     } else if (warp < RS_MMA_WARP) {
@@ -327,8 +325,13 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 #define UNP_STAMP(code) do { } while (0)
 #endif
         uint64_t za_pack[4] = {0, 0, 0, 0};               // zero-points of this thread's four U rows, one byte per group
+        int sm = strip0, nt = nt0;
         for (int tile = t_begin; tile < t_end; ++tile) {
-            const int strip = tile / tiles_n;
+            const int strip = sm;
+            if (++nt == tiles_n) {
+                nt = 0;
+                ++sm;
+            }
             if (strip != cur_strip) {
                 cur_strip = strip;
                 const int m0 = strip << 7;
@@ -385,16 +388,19 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 UNP_STAMP(0x1300 | g);
             }
         }
-    } else if (warp == RS_MMA_WARP) {
+    } else {
+    if (warp == RS_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t it = 0, bi = 0, k = 0;
 #ifdef ADE_TRACE
             int tcn = 0;
 #endif
+            int nt = nt0;
             for (int tile = t_begin; tile < t_end; ++tile) {
-                const bool first = tile == t_begin || tile % tiles_n == 0;
-                const bool last = tile == t_end - 1 || (tile + 1) % tiles_n == 0;
+                const bool first = tile == t_begin || nt == 0;
+                const bool last = tile == t_end - 1 || nt + 1 == tiles_n;
+                if (++nt == tiles_n) nt = 0;
                 for (int g = 0; g < ng; ++g, ++it, ++bi) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                     const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
@@ -429,8 +435,13 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
 #ifdef ADE_TRACE
             int tcn = 0;
 #endif
+            int sm = strip0, nt = nt0;
             for (int tile = t_begin; tile < t_end; ++tile) {
-                const int strip = tile / tiles_n, n0 = (tile % tiles_n) << 7;
+                const int strip = sm, n0 = nt << 7;
+                if (++nt == tiles_n) {
+                    nt = 0;
+                    ++sm;
+                }
                 if (strip != cur_strip) {
                     cur_strip = strip;
                     for (int g = 0; g < ng; ++g, ++ri) {
@@ -452,11 +463,15 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp == RS_SCALE_WARP) {
         // ------------------------------------------------------------------ scale tables, one tile ahead
-        int j = 0;
+        int j = 0, sm = strip0, nt = nt0;
         for (int tile = t_begin; tile < t_end; ++tile, ++j) {
-            const int m0 = (tile / tiles_n) << 7, n0 = (tile % tiles_n) << 7;
+            const int m0 = sm << 7, n0 = nt << 7;
+            if (++nt == tiles_n) {
+                nt = 0;
+                ++sm;
+            }
             const uint32_t b = j & 1, jph = (j >> 1) & 1;
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);
             // us: rows m0.. of a (M, ng) array = 128 * ng consecutive bf16; vs: 128 consecutive bf16 per group
@@ -503,6 +518,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::BAR_SC_FULL + b));
         }
+    }
     }
 
     drain_after_abort(abort_flag);

@@ -255,6 +255,18 @@ def decode_section(torch, dev, peak, arch="7b", batch=1, prompt=64, new=128, see
     per_token = tg["decode_ms"] * 1e-3 / (new - 1)
     eager_per_token = te["decode_ms"] * 1e-3 / n_eager
     t_prefill = tg["prefill_ms"] * 1e-3
+    # the delta-carrying linear modules alone, same call sequence as one decode step, replayed from a graph: what part
+    # of a token is this path's own, and what part is the rest of the Hugging Face layer (norms, rotary embedding,
+    # attention, cache update, head)
+    calls = []
+    for layer in model.model.layers:
+        xh = torch.randn(batch, 1, cfg.hidden_size, device=dev, dtype=torch.bfloat16)
+        xi = torch.randn(batch, 1, cfg.intermediate_size, device=dev, dtype=torch.bfloat16)
+        att, mlp = layer.self_attn, layer.mlp
+        for m, xin in ((att.q_proj, xh), (att.k_proj, xh), (att.v_proj, xh), (att.o_proj, xh), (mlp.gate_proj, xh), (mlp.up_proj, xh),
+                       (mlp.down_proj, xi)):
+            calls.append(lambda m=m, xin=xin: m(xin))
+    linear_ms = time_graph_calls(torch, calls, reps=5) * len(calls) / 1e3
     # bytes the decode step has to stream once per token: every linear weight, the delta (codes, scales, zero-points,
     # with V^T counted once), the output head; the KV cache of <= 192 positions is below 0.1 GB and left out
     h, inter, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
@@ -269,6 +281,7 @@ def decode_section(torch, dev, peak, arch="7b", batch=1, prompt=64, new=128, see
                   f"batch {batch}, prompt {prompt}, {new} greedy tokens, factored path, decode step replayed from a CUDA graph",
         "layers": L, "tokens_per_s": batch / per_token, "ms_per_token": per_token * 1e3,
         "eager_tokens_per_s": batch / eager_per_token, "eager_us_per_module_call": eager_per_token * 1e6 / len(ranks),
+        "delta_modules_ms_per_token": linear_ms, "rest_of_model_ms_per_token": per_token * 1e3 - linear_ms,
         "prefill_ms": t_prefill * 1e3, "bytes_per_token": total, "ceiling_tokens_per_s": ceiling,
         "frac_of_ceiling": batch / per_token / ceiling,
         "tokens_equal_eager": bool((out[:, :prompt + n_eager + 1] == eager).all()), "fused_groups": groups, "model_build_s": build_s,

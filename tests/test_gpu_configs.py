@@ -289,7 +289,7 @@ def test_full_size_7b_decoder_layer_against_merged_weights():
         torch.cuda.synchronize()
         kernels.check_factored_status(DEV)
         for prefix, (xin, yout) in seen.items():
-            W = ref.get_submodule(prefix).weight.float()
+            W = ref.get_submodule(prefix).weight.detach().float()
             want = (xin.reshape(-1, xin.shape[-1]).float() @ W.t()).cpu().numpy()
             err, cos = O.parity(yout.reshape(want.shape).float().cpu().numpy(), want)
             assert err <= 1e-2 and cos >= 0.9999, (T, prefix, err, cos)
