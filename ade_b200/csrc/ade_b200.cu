@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "compress.cuh"
+#include "decode_ops.cuh"
 #include "factored.cuh"
 #include "recon.cuh"
 #include "recon_strip.cuh"
@@ -461,6 +462,39 @@ int ade_b200_compress_rows(const float* x, const float* sqrt_s, uint8_t* codes, 
     __nv_bfloat16* zp = reinterpret_cast<__nv_bfloat16*>(zero);
     if (transposed) ade::compress_rows_kernel<true><<<grid, ade::CQ_THREADS, smem, st>>>(x, sqrt_s, codes, sc, zp, rows, r, rotate);
     else ade::compress_rows_kernel<false><<<grid, ade::CQ_THREADS, smem, st>>>(x, sqrt_s, codes, sc, zp, rows, r, rotate);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+int ade_b200_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, long long x_row_stride, float eps, void* stream) {
+    if (!x || !weight || !out) return ADE_ERR_NULL;
+    if (rows < 1 || H < 1 || x_row_stride < H) return ADE_ERR_SHAPE;
+    ade::rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), H, x_row_stride, eps);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out, int B, int T, int q_heads,
+                  int k_heads, int head_dim, long long q_row_stride, long long k_row_stride, long long cs_batch_stride, void* stream) {
+    if (!q || !k || !cos_t || !sin_t || !q_out || !k_out) return ADE_ERR_NULL;
+    if (B < 1 || T < 1 || q_heads < 1 || k_heads < 1 || head_dim < 2 || (head_dim & 1)) return ADE_ERR_SHAPE;
+    const long long total = static_cast<long long>(B) * T * (q_heads + k_heads) * head_dim;
+    const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    ade::rope_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(cos_t),
+        static_cast<const __nv_bfloat16*>(sin_t), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), B, T, q_heads,
+        k_heads, head_dim, q_row_stride, k_row_stride, cs_batch_stride);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, long long gate_row_stride, long long up_row_stride,
+                      void* stream) {
+    if (!gate || !up || !out) return ADE_ERR_NULL;
+    if (rows < 1 || cols < 1 || gate_row_stride < cols || up_row_stride < cols) return ADE_ERR_SHAPE;
+    const long long total = static_cast<long long>(rows) * cols;
+    const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    ade::silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), rows, cols,
+        gate_row_stride, up_row_stride);
     return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
 

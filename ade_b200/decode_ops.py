@@ -1,0 +1,114 @@
+"""Fused elementwise operations of a LLaMA decoder layer for the token-by-token decode step.
+
+``enable_fused_decode_ops(model)`` swaps three pieces of a transformers LLaMA model for single CUDA launches of the C
+ABI (``ade_b200_rmsnorm``, ``ade_b200_rope``, ``ade_b200_silu_mul``): RMSNorm, the rotary position embedding of q and k,
+and SiLU(gate) * up.  The arithmetic and the bfloat16 roundings are those of the torch operations they replace, so the
+logits do not move; what changes is the number of kernels per token (about forty per layer fewer), which at decode
+sizes is what the time outside the delta application consists of.  They apply to small inputs only (at most
+``MAX_ROWS`` token rows); longer inputs, other dtypes and CPU tensors take the original code.
+
+The reference has no counterpart: it generates with ``model.generate`` of transformers (src/evaluate.py:241).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+MAX_ROWS = 512          # token rows (batch * sequence) up to which the fused kernels are used
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rows_ok(t: torch.Tensor, rows: int) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and 0 < rows <= MAX_ROWS
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """LlamaRMSNorm.forward for a bfloat16 CUDA tensor whose last dimension is contiguous."""
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], H), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().ade_b200_rmsnorm(x2.data_ptr(), weight.data_ptr(), out.data_ptr(), x2.shape[0], H, x2.stride(0), float(eps),
+                                            _stream()), "ade_b200_rmsnorm")
+    return out.view(x.shape)
+
+
+def rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+    """apply_rotary_pos_emb for q (B, heads, T, hd) and k given as transposed views of (B, T, heads, hd) projections;
+    returns contiguous (B, heads, T, hd) tensors."""
+    B, hq, T, hd = q.shape
+    hk = k.shape[1]
+    qo = torch.empty((B, hq, T, hd), dtype=torch.bfloat16, device=q.device)
+    ko = torch.empty((B, hk, T, hd), dtype=torch.bfloat16, device=q.device)
+    cs_stride = 0 if cos.shape[0] == 1 else T * hd
+    _lib.check(_lib.load().ade_b200_rope(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), ko.data_ptr(), B, T, hq, hk,
+                                         hd, q.stride(2), k.stride(2), cs_stride, _stream()), "ade_b200_rope")
+    return qo, ko
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """act_fn(gate) * up for SiLU, bfloat16, last dimension contiguous (row strides free)."""
+    cols = gate.shape[-1]
+    g2, u2 = gate.reshape(-1, cols), up.reshape(-1, cols)
+    out = torch.empty((g2.shape[0], cols), dtype=torch.bfloat16, device=gate.device)
+    _lib.check(_lib.load().ade_b200_silu_mul(g2.data_ptr(), u2.data_ptr(), out.data_ptr(), g2.shape[0], cols, g2.stride(0), u2.stride(0),
+                                             _stream()), "ade_b200_silu_mul")
+    return out.view(*gate.shape[:-1], cols)
+
+
+def _rope_layout_ok(x: torch.Tensor) -> bool:
+    """(B, heads, T, hd) view of a (B, T, heads, hd) projection: head_dim contiguous, heads hd apart, batch rows T apart."""
+    B, h, T, hd = x.shape
+    return x.stride(3) == 1 and x.stride(1) == hd and (B == 1 or x.stride(0) == T * x.stride(2))
+
+
+def enable_fused_decode_ops(model) -> int:
+    """Patch `model` (a transformers LLaMA-architecture causal LM) in place; returns the number of modules patched.
+    The rotary embedding is a module-level function of transformers' LLaMA implementation, so that patch is
+    process-wide (it falls back to the original for anything but small bfloat16 CUDA inputs)."""
+    from transformers.models.llama import modeling_llama as ml
+
+    if not getattr(ml, "_ade_rope_patched", False):
+        original = ml.apply_rotary_pos_emb
+
+        def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
+            if (unsqueeze_dim == 1 and q.dim() == 4 and _rows_ok(q, q.shape[0] * q.shape[2]) and k.dtype == torch.bfloat16
+                    and cos.dtype == torch.bfloat16 and cos.dim() == 3 and cos.is_contiguous() and sin.is_contiguous()
+                    and cos.shape[0] in (1, q.shape[0]) and _rope_layout_ok(q) and _rope_layout_ok(k)):
+                return rope(q, k, cos, sin)
+            return original(q, k, cos, sin, unsqueeze_dim)
+
+        ml.apply_rotary_pos_emb = apply_rotary_pos_emb
+        ml._ade_rope_patched = True
+    n = 0
+    for mod in model.modules():
+        if isinstance(mod, ml.LlamaRMSNorm) and not hasattr(mod, "_ade_orig_forward"):
+            mod._ade_orig_forward = mod.forward
+
+            def norm_forward(x, mod=mod):
+                if _rows_ok(x, x.numel() // x.shape[-1]) and x.stride(-1) == 1 and mod.weight.dtype == torch.bfloat16:
+                    return rmsnorm(x, mod.weight, mod.variance_epsilon)
+                return mod._ade_orig_forward(x)
+
+            mod.forward = norm_forward
+            n += 1
+        elif (isinstance(mod, ml.LlamaMLP) and not hasattr(mod, "_ade_orig_forward")
+              and type(mod.act_fn).__name__ in ("SiLU", "SiLUActivation")):
+            mod._ade_orig_forward = mod.forward
+
+            def mlp_forward(x, mod=mod):
+                if _rows_ok(x, x.numel() // x.shape[-1]):
+                    g, u = mod.gate_proj(x), mod.up_proj(x)
+                    if g.dtype == torch.bfloat16 and g.stride(-1) == 1 and u.stride(-1) == 1:
+                        return mod.down_proj(silu_mul(g, u))
+                    return mod.down_proj(mod.act_fn(g) * u)
+                return mod._ade_orig_forward(x)
+
+            mod.forward = mlp_forward
+            n += 1
+    return n

@@ -121,11 +121,12 @@ LLAMA_ARCH = {
 }
 
 
-def synthetic_llama(arch="7b", layers=None, seed=0, device="cuda", vocab=32000, fuse=True, alpha=1.0 / 16):
+def synthetic_llama(arch="7b", layers=None, seed=0, device="cuda", vocab=32000, fuse=True, alpha=1.0 / 16, fused_ops=True):
     """Random-init bfloat16 LLaMA-architecture model with a synthetic delta on every linear module, each an
     ``ADEKernelLinear`` (configs 2-4 of the benchmark; no checkpoint or dataset is involved).  Ranks are drawn for
-    the alpha bit budget (``draw_ranks``), packed fields directly on the device (``random_packed``).  Returns
-    (model, ranks, number of fused q/k/v and gate/up groups)."""
+    the alpha bit budget (``draw_ranks``), packed fields directly on the device (``random_packed``).  q/k/v and gate/up
+    of every layer are served by one launch each (`fuse`), RMSNorm / rotary embedding / SiLU product by one launch each
+    (`fused_ops`).  Returns (model, ranks, number of fused q/k/v and gate/up groups)."""
     from transformers import LlamaConfig, LlamaForCausalLM
 
     from .serving import LINEAR_MODULE_NAMES, ADEKernelLinear, fuse_kernel_linears
@@ -152,4 +153,8 @@ def synthetic_llama(arch="7b", layers=None, seed=0, device="cuda", vocab=32000, 
             setattr(parent, leaf, ADEKernelLinear(lin.weight.data, packed))
             i += 1
     groups = fuse_kernel_linears(model) if fuse else 0
+    if fused_ops:
+        from .decode_ops import enable_fused_decode_ops
+
+        enable_fused_decode_ops(model)
     return model, ranks, groups

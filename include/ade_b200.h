@@ -218,6 +218,26 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
                    int32_t* dbg_acc, int* status_dev, void* stream);
 
 /*
+ * Elementwise pieces of a LLaMA decoder layer at decode sizes, one launch each.  No counterpart in the reference, which
+ * leaves them to transformers (src/evaluate.py:241 calls model.generate): there an RMSNorm is eight elementwise
+ * kernels, the rotary embedding fourteen, SiLU and product two, and inside a CUDA graph of the decode step they cost
+ * more than the delta application they surround.  Same arithmetic and the same bfloat16 roundings as the torch
+ * operations they stand in for; all tensors bfloat16, strides in elements.
+ *   ade_b200_rmsnorm   out[t][:] = weight * bf16(x[t][:] * rsqrt(mean(x[t][:]^2) + eps)), float32 statistics.
+ *   ade_b200_rope      q [B][T][q_heads][head_dim] and k [B][T][k_heads][head_dim], given with their row strides (the
+ *                      projections may be column slices of one fused output), rotated with cos / sin [B or 1][T][head_dim]
+ *                      (cs_batch_stride = T * head_dim, or 0 for one shared table) into q_out [B][q_heads][T][head_dim]
+ *                      and k_out [B][k_heads][T][head_dim]: x cos + rotate_half(x) sin.
+ *   ade_b200_silu_mul  out[r][c] = bf16(silu(gate[r][c])) * up[r][c]; out contiguous [rows][cols].
+ */
+int ade_b200_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, long long x_row_stride, float eps, void* stream);
+int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out, int B, int T,
+                  int q_heads, int k_heads, int head_dim, long long q_row_stride, long long k_row_stride, long long cs_batch_stride,
+                  void* stream);
+int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, long long gate_row_stride,
+                      long long up_row_stride, void* stream);
+
+/*
  * Process-wide options.  No counterpart in the reference.
  *   ADE_OPT_WAIT_LIMIT_CYCLES   clock cycles a wait inside a kernel (for h, for an operand stage, ...) may take
  *                               before the kernel gives up, records its status and runs to its end; 0 restores the
