@@ -46,8 +46,11 @@ def rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor)
     qo = torch.empty((B, hq, T, hd), dtype=torch.bfloat16, device=q.device)
     ko = torch.empty((B, hk, T, hd), dtype=torch.bfloat16, device=q.device)
     cs_stride = 0 if cos.shape[0] == 1 else T * hd
+    # distance between consecutive (batch, token) rows of the projection; a dimension of size 1 reports an arbitrary stride
+    rq = q.stride(2) if T > 1 else q.stride(0)
+    rk = k.stride(2) if T > 1 else k.stride(0)
     _lib.check(_lib.load().ade_b200_rope(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), ko.data_ptr(), B, T, hq, hk,
-                                         hd, q.stride(2), k.stride(2), cs_stride, _stream()), "ade_b200_rope")
+                                         hd, rq, rk, cs_stride, _stream()), "ade_b200_rope")
     return qo, ko
 
 
@@ -64,7 +67,7 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 def _rope_layout_ok(x: torch.Tensor) -> bool:
     """(B, heads, T, hd) view of a (B, T, heads, hd) projection: head_dim contiguous, heads hd apart, batch rows T apart."""
     B, h, T, hd = x.shape
-    return x.stride(3) == 1 and x.stride(1) == hd and (B == 1 or x.stride(0) == T * x.stride(2))
+    return x.stride(3) == 1 and (h == 1 or x.stride(1) == hd) and (B == 1 or T == 1 or x.stride(0) == T * x.stride(2))
 
 
 def enable_fused_decode_ops(model) -> int:
