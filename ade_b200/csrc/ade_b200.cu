@@ -498,6 +498,24 @@ int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int
     return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
 
+int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void* cos_t, const void* sin_t, const void* mask, void* k_cache,
+                         void* v_cache, const long long* pos, void* out, int B, int q_heads, int k_heads, int head_dim, int cache_len,
+                         long long q_row_stride, long long k_row_stride, long long v_row_stride, long long cs_batch_stride,
+                         long long mask_row_stride, float scale, void* stream) {
+    if (!q || !k || !v || !cos_t || !sin_t || !k_cache || !v_cache || !pos || !out) return ADE_ERR_NULL;
+    if (B < 1 || q_heads < 1 || k_heads < 1 || q_heads % k_heads || cache_len < 1) return ADE_ERR_SHAPE;
+    if (head_dim < 32 || head_dim > 256 || head_dim % 32) return ADE_ERR_SHAPE;
+    if (!aligned16(k_cache) || !aligned16(v_cache)) return ADE_ERR_ALIGN;
+    const size_t smem = (static_cast<size_t>(7) * head_dim + cache_len) * sizeof(float);
+    if (smem > 48 * 1024) return ADE_ERR_SHAPE;                           // cache lengths up to about 10 000 positions
+    ade::attn_decode_kernel<<<B * q_heads, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+        static_cast<const __nv_bfloat16*>(cos_t), static_cast<const __nv_bfloat16*>(sin_t), static_cast<const bool*>(mask),
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), pos, static_cast<__nv_bfloat16*>(out), q_heads, k_heads,
+        head_dim, cache_len, q_row_stride, k_row_stride, v_row_stride, cs_batch_stride, mask_row_stride, scale);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
 int ade_b200_factored_static_status(int* dst, int clear, void* stream) {
     if (!dst) return ADE_ERR_NULL;
     char* base = nullptr;

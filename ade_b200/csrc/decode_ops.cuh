@@ -4,8 +4,9 @@
 // elementwise kernels around the four launches of the factored kernel (RMSNorm: 8 each, rotary embedding: 14, SiLU
 // and product: 2), and inside a CUDA graph every one of them costs about as much as it would take to stream a
 // megabyte of weights.  The three kernels here do the same arithmetic with the same bfloat16 roundings in one launch
-// each, so that tokens/s measures the weight stream and not the launch count.  No counterpart in the reference, which
-// leaves these operations to transformers (src/evaluate.py:241 calls model.generate).
+// each, so that tokens/s measures the weight stream and not the launch count; a fourth does the single-token attention
+// step (rotary embedding, KV-cache write, attention) in one launch.  No counterpart in the reference, which leaves
+// these operations to transformers (src/evaluate.py:241 calls model.generate).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -81,6 +82,128 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ g, const __nv_
         const float x = __bfloat162float(g[r * g_stride + c]);
         const float s = bf16r(x / (1.0f + expf(-x)));
         out[e] = __float2bfloat16_rn(s * __bfloat162float(u[r * u_stride + c]));
+    }
+}
+
+// One decode step of attention for one new token per sequence: rotary embedding of q and k, the write of k and v into
+// the static KV cache at position *pos, and softmax(q K^T * scale) V over the cache positions the mask allows, in one
+// launch (transformers runs the rotary embedding, two index_copy_ calls with their index arithmetic and scaled dot
+// product attention as about twenty kernels here).  One CTA of 128 threads per (sequence, query head).
+//   q [B][hq*hd], k / v [B][hk*hd] with row strides (column slices of a fused q/k/v output); cos / sin [B or 1][hd];
+//   kc / vc: the cache, [B][hk][L][hd] contiguous; mask: bool [B][L], true = attend (it includes position *pos), or
+//   nullptr = attend to positions 0 .. *pos; out [B][hq*hd] contiguous.
+// The new k (rotated, rounded to bfloat16 as the cache stores it) and v are used from registers for position *pos, so
+// no CTA reads what another one writes in the same launch; the CTA of the first query head of every KV group writes
+// them to the cache.  Scores, softmax and the weighted sum are float32.
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                           const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ cs,
+                                                           const __nv_bfloat16* __restrict__ sn, const bool* __restrict__ mask,
+                                                           __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                                                           const long long* __restrict__ pos, __nv_bfloat16* __restrict__ out, int hq, int hk,
+                                                           int hd, int L, long long q_stride, long long k_stride, long long v_stride,
+                                                           long long cs_batch_stride, long long mask_stride, float scale) {
+    extern __shared__ float at_smem[];
+    float* qs = at_smem;              // [hd] rotated q
+    float* kn = qs + hd;              // [hd] rotated new k (bfloat16 values)
+    float* vn = kn + hd;              // [hd] new v
+    float* red = vn + hd;             // [4 warps][hd] partial sums / [128] reductions
+    float* sc = red + 4 * hd;         // [L] scores, then weights
+    const int b = blockIdx.x / hq, h = blockIdx.x % hq;
+    const int group = hq / hk, kvh = h / group;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p0 = static_cast<int>(*pos);
+    const int half = hd >> 1;
+    const __nv_bfloat16* qr = q + static_cast<size_t>(b) * q_stride + h * hd;
+    const __nv_bfloat16* kr = k + static_cast<size_t>(b) * k_stride + kvh * hd;
+    const __nv_bfloat16* vr = v + static_cast<size_t>(b) * v_stride + kvh * hd;
+    __nv_bfloat16* kcb = kc + (static_cast<size_t>(b) * hk + kvh) * L * hd;
+    __nv_bfloat16* vcb = vc + (static_cast<size_t>(b) * hk + kvh) * L * hd;
+    for (int d = tid; d < hd; d += 128) {
+        const float c = __bfloat162float(cs[static_cast<size_t>(b) * cs_batch_stride + d]);
+        const float s = __bfloat162float(sn[static_cast<size_t>(b) * cs_batch_stride + d]);
+        const int od = d < half ? d + half : d - half;
+        const float sign = d < half ? -1.f : 1.f;
+        qs[d] = bf16r(bf16r(__bfloat162float(qr[d]) * c) + bf16r(sign * __bfloat162float(qr[od]) * s));
+        kn[d] = bf16r(bf16r(__bfloat162float(kr[d]) * c) + bf16r(sign * __bfloat162float(kr[od]) * s));
+        vn[d] = __bfloat162float(vr[d]);
+        if (h % group == 0 && p0 >= 0 && p0 < L) {
+            kcb[static_cast<size_t>(p0) * hd + d] = __float2bfloat16_rn(kn[d]);
+            vcb[static_cast<size_t>(p0) * hd + d] = vr[d];
+        }
+    }
+    __syncthreads();
+    // scores: one cache position per thread and pass
+    const bool* mb = mask ? mask + static_cast<size_t>(b) * mask_stride : nullptr;
+    float mx = -3.0e38f;
+    int hi = 0;                                            // one past the last attended position
+    for (int p = tid; p < L; p += 128) {
+        const bool on = mb ? mb[p] : p <= p0;
+        float s = -3.0e38f;
+        if (on) {
+            float a = 0.f;
+            if (p == p0) {
+                for (int d = 0; d < hd; ++d) a += qs[d] * kn[d];
+            } else {
+                const uint4* row = reinterpret_cast<const uint4*>(kcb + static_cast<size_t>(p) * hd);
+                for (int c8 = 0; c8 < (hd >> 3); ++c8) {
+                    const uint4 w = row[c8];
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        a += qs[c8 * 8 + 2 * e] * __uint_as_float(ww[e] << 16);
+                        a += qs[c8 * 8 + 2 * e + 1] * __uint_as_float(ww[e] & 0xFFFF0000u);
+                    }
+                }
+            }
+            s = a * scale;
+            hi = p + 1;
+        }
+        sc[p] = s;
+        mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        hi = max(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o));
+    }
+    if (lane == 0) {
+        red[warp] = mx;
+        red[4 + warp] = static_cast<float>(hi);
+    }
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    hi = static_cast<int>(fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
+    __syncthreads();
+    float sum = 0.f;
+    for (int p = tid; p < hi; p += 128) {
+        const float w = sc[p] > -1.0e38f ? expf(sc[p] - mx) : 0.f;
+        sc[p] = w;
+        sum += w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = red[0] + red[1] + red[2] + red[3];
+    __syncthreads();
+    // weighted sum of v: warp w takes positions w, w + 4, ...; a lane owns hd / 32 consecutive dimensions
+    const int per = hd >> 5;                               // 2, 4 or 8
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = warp; p < hi; p += 4) {
+        const float w = sc[p];
+        if (w == 0.f) continue;
+        if (p == p0) {
+            for (int i = 0; i < per; ++i) acc[i] += w * vn[lane * per + i];
+        } else {
+            const __nv_bfloat16* row = vcb + static_cast<size_t>(p) * hd + lane * per;
+            for (int i = 0; i < per; ++i) acc[i] += w * __bfloat162float(row[i]);
+        }
+    }
+    for (int i = 0; i < per; ++i) red[warp * hd + lane * per + i] = acc[i];
+    __syncthreads();
+    for (int d = tid; d < hd; d += 128) {
+        const float o = (red[d] + red[hd + d] + red[2 * hd + d] + red[3 * hd + d]) / sum;
+        out[(static_cast<size_t>(b) * hq + h) * hd + d] = __float2bfloat16_rn(o);
     }
 }
 

@@ -1,10 +1,13 @@
 """Fused elementwise operations of a LLaMA decoder layer for the token-by-token decode step.
 
-``enable_fused_decode_ops(model)`` swaps three pieces of a transformers LLaMA model for single CUDA launches of the C
-ABI (``ade_b200_rmsnorm``, ``ade_b200_rope``, ``ade_b200_silu_mul``): RMSNorm, the rotary position embedding of q and k,
-and SiLU(gate) * up.  The arithmetic and the bfloat16 roundings are those of the torch operations they replace, so the
-logits do not move; what changes is the number of kernels per token (about forty per layer fewer), which at decode
-sizes is what the time outside the delta application consists of.  They apply to small inputs only (at most
+``enable_fused_decode_ops(model)`` swaps pieces of a transformers LLaMA model for single CUDA launches of the C
+ABI: RMSNorm (``ade_b200_rmsnorm``), the rotary position embedding of q and k (``ade_b200_rope``), SiLU(gate) * up
+(``ade_b200_silu_mul``) and, for single-token steps on a static KV cache, the whole attention step: rotary embedding,
+cache write and attention (``ade_b200_attn_decode``).  The arithmetic and the bfloat16 roundings of the first three
+are those of the torch operations they replace, so the logits do not move; the attention step keeps scores and
+sums in float32 where torch's fused attention rounds the probabilities to bfloat16, a difference below the
+tolerance of the path.  What changes is the number of kernels per token (about sixty per layer fewer), which at
+decode sizes is what the time outside the delta application consists of.  They apply to small inputs only (at most
 ``MAX_ROWS`` token rows); longer inputs, other dtypes and CPU tensors take the original code.
 
 The reference has no counterpart: it generates with ``model.generate`` of transformers (src/evaluate.py:241).
@@ -64,6 +67,43 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out.view(*gate.shape[:-1], cols)
 
 
+def attn_decode(q, k, v, cos, sin, mask, layer, scale: float) -> torch.Tensor:
+    """Single-token attention step on a static cache layer: q (B, 1, hq*hd), k / v (B, 1, hk*hd) straight from the
+    projections, cos / sin (B or 1, 1, hd), mask None or bool (B, 1, 1, L).  Writes k, v into the layer's cache at its
+    running position, advances that position, returns (B, 1, hq*hd)."""
+    B = q.shape[0]
+    hk, L, hd = layer.keys.shape[1], layer.keys.shape[2], layer.keys.shape[3]
+    hq = q.shape[-1] // hd
+    out = torch.empty((B, 1, hq * hd), dtype=torch.bfloat16, device=q.device)
+    row = lambda t: t.stride(0) if B > 1 else t.shape[-1]
+    _lib.check(_lib.load().ade_b200_attn_decode(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), None if mask is None else mask.data_ptr(),
+        layer.keys.data_ptr(), layer.values.data_ptr(), layer.cumulative_length.data_ptr(), out.data_ptr(), B, hq, hk, hd, L,
+        row(q), row(k), row(v), 0 if cos.shape[0] == 1 else hd, 0 if mask is None else mask.stride(0), float(scale), _stream()),
+        "ade_b200_attn_decode")
+    layer.cumulative_length.add_(1)
+    return out
+
+
+def _attn_decode_ok(mod, x, cos, mask, layer) -> bool:
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.shape[1] == 1 and not mod.training):
+        return False
+    if type(layer).__name__ != "StaticLayer" or not getattr(layer, "is_initialized", False):
+        return False
+    kc = layer.keys
+    if not (kc.dtype == torch.bfloat16 and kc.is_contiguous() and layer.values.is_contiguous() and kc.shape[0] == x.shape[0]):
+        return False
+    hd = kc.shape[3]
+    if hd % 32 or hd > 256 or (7 * hd + kc.shape[2]) * 4 > 48 * 1024 or layer.cumulative_length.dtype != torch.int64:
+        return False
+    if not (cos.dtype == torch.bfloat16 and cos.dim() == 3 and cos.shape[1] == 1 and cos.is_contiguous() and cos.shape[0] in (1, x.shape[0])):
+        return False
+    if mask is not None and not (mask.dtype == torch.bool and mask.dim() == 4 and mask.shape[1] == 1 and mask.shape[2] == 1
+                                 and mask.shape[3] == kc.shape[2] and mask.stride(3) == 1 and mask.shape[0] == x.shape[0]):
+        return False
+    return True
+
+
 def _rope_layout_ok(x: torch.Tensor) -> bool:
     """(B, heads, T, hd) view of a (B, T, heads, hd) projection: head_dim contiguous, heads hd apart, batch rows T apart."""
     B, h, T, hd = x.shape
@@ -90,7 +130,24 @@ def enable_fused_decode_ops(model) -> int:
         ml._ade_rope_patched = True
     n = 0
     for mod in model.modules():
-        if isinstance(mod, ml.LlamaRMSNorm) and not hasattr(mod, "_ade_orig_forward"):
+        if isinstance(mod, ml.LlamaAttention) and not hasattr(mod, "_ade_orig_forward"):
+            mod._ade_orig_forward = mod.forward
+
+            def attn_forward(hidden_states, position_embeddings=None, attention_mask=None, past_key_values=None, mod=mod, **kw):
+                layers = getattr(past_key_values, "layers", None)
+                layer = layers[mod.layer_idx] if layers is not None and mod.layer_idx < len(layers) else None
+                if (position_embeddings is not None and layer is not None
+                        and _attn_decode_ok(mod, hidden_states, position_embeddings[0], attention_mask, layer)):
+                    q, k, v = mod.q_proj(hidden_states), mod.k_proj(hidden_states), mod.v_proj(hidden_states)
+                    if all(t.dtype == torch.bfloat16 and t.stride(-1) == 1 for t in (q, k, v)) and position_embeddings[1].is_contiguous():
+                        ctx = attn_decode(q, k, v, position_embeddings[0], position_embeddings[1], attention_mask, layer, mod.scaling)
+                        return mod.o_proj(ctx), None
+                return mod._ade_orig_forward(hidden_states, position_embeddings=position_embeddings, attention_mask=attention_mask,
+                                             past_key_values=past_key_values, **kw)
+
+            mod.forward = attn_forward
+            n += 1
+        elif isinstance(mod, ml.LlamaRMSNorm) and not hasattr(mod, "_ade_orig_forward"):
             mod._ade_orig_forward = mod.forward
 
             def norm_forward(x, mod=mod):

@@ -229,6 +229,12 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
  *                      (cs_batch_stride = T * head_dim, or 0 for one shared table) into q_out [B][q_heads][T][head_dim]
  *                      and k_out [B][k_heads][T][head_dim]: x cos + rotate_half(x) sin.
  *   ade_b200_silu_mul  out[r][c] = bf16(silu(gate[r][c])) * up[r][c]; out contiguous [rows][cols].
+ *   ade_b200_attn_decode  one new token per sequence: rotary embedding of q [B][q_heads*head_dim] and k, write of k and v
+ *                      ([B][k_heads*head_dim], row strides free) into the static KV cache ([B][k_heads][cache_len][head_dim],
+ *                      contiguous) at position *pos (device int64), and softmax(q K^T scale) V over the positions that
+ *                      mask (bool [B][cache_len], true = attend, includes *pos; NULL = positions 0..*pos) allows, written to
+ *                      out [B][q_heads*head_dim].  Scores and sums in float32.  q_heads % k_heads == 0, head_dim a multiple
+ *                      of 32 up to 256, (7 head_dim + cache_len) floats of shared memory <= 48 KB.  *pos is not advanced.
  */
 int ade_b200_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, long long x_row_stride, float eps, void* stream);
 int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out, int B, int T,
@@ -236,6 +242,10 @@ int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* s
                   void* stream);
 int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, long long gate_row_stride,
                       long long up_row_stride, void* stream);
+int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void* cos_t, const void* sin_t, const void* mask,
+                         void* k_cache, void* v_cache, const long long* pos, void* out, int B, int q_heads, int k_heads,
+                         int head_dim, int cache_len, long long q_row_stride, long long k_row_stride, long long v_row_stride,
+                         long long cs_batch_stride, long long mask_row_stride, float scale, void* stream);
 
 /*
  * Process-wide options.  No counterpart in the reference.

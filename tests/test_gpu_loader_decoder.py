@@ -152,7 +152,7 @@ def test_fused_decode_ops_in_the_model():
     with torch.no_grad():
         before = model(ids).logits.float()
         tokens_before = GreedyGraphDecoder(model).generate(ids, 12)
-    assert decode_ops.enable_fused_decode_ops(model) == 2 * 2 + 1 + 2          # two norms per layer, the final norm, two MLPs
+    assert decode_ops.enable_fused_decode_ops(model) == 2 * 2 + 1 + 2 + 2      # two norms per layer, the final norm, two MLPs, two attentions
     assert decode_ops.enable_fused_decode_ops(model) == 0                      # idempotent
     with torch.no_grad():
         after = model(ids).logits.float()
@@ -161,3 +161,46 @@ def test_fused_decode_ops_in_the_model():
         assert model(long_ids).logits.shape == (1, 600, 512)
     assert float((after - before).abs().max()) <= 2e-2 * float(before.abs().max())
     assert (tokens_after == tokens_before).float().mean().item() >= 0.9
+
+
+def test_attention_decode_step_against_torch():
+    """The fused single-token attention step (rotary embedding, cache write, attention) against the same step done with
+    torch operations on a static cache: grouped-query heads, a padded batch (masked positions), several steps in a
+    row so that the cache written by one step is read by the next."""
+    from types import SimpleNamespace
+
+    from ade_b200 import decode_ops
+
+    g = torch.Generator().manual_seed(7)
+    for B, hq, hk, hd, L, start in [(1, 32, 32, 128, 193, 64), (3, 8, 2, 64, 40, 5), (2, 40, 40, 128, 64, 0)]:
+        keys = torch.zeros(B, hk, L, hd, dtype=torch.bfloat16, device=DEV)
+        vals = torch.zeros_like(keys)
+        if start:
+            keys[:, :, :start] = torch.randn(B, hk, start, hd, generator=g).to(torch.bfloat16).to(DEV)
+            vals[:, :, :start] = torch.randn(B, hk, start, hd, generator=g).to(torch.bfloat16).to(DEV)
+        rk, rv = keys.clone(), vals.clone()
+        layer = SimpleNamespace(keys=keys, values=vals, cumulative_length=torch.tensor([start], device=DEV), is_initialized=True)
+        scale = hd ** -0.5
+        for step in range(3):
+            pos = start + step
+            y = torch.randn(B, (hq + 2 * hk) * hd, generator=g).to(torch.bfloat16).to(DEV)         # fused q/k/v output
+            q, k, v = (t.unsqueeze(1) for t in (y[:, :hq * hd], y[:, hq * hd:(hq + hk) * hd], y[:, (hq + hk) * hd:]))
+            ang = torch.rand(1, 1, hd, generator=g) * 6.28
+            cos, sin = ang.cos().to(torch.bfloat16).to(DEV), ang.sin().to(torch.bfloat16).to(DEV)
+            mask = torch.zeros(B, 1, 1, L, dtype=torch.bool, device=DEV)
+            mask[..., :pos + 1] = True
+            if B > 1:
+                mask[1, ..., :min(2, pos)] = False                                                  # left padding of one row
+            got = decode_ops.attn_decode(q, k, v, cos, sin, mask if step != 1 or B > 1 else None, layer, scale)
+            # the same step with torch operations
+            q4, k4, v4 = q.view(B, 1, hq, hd).transpose(1, 2), k.view(B, 1, hk, hd).transpose(1, 2), v.view(B, 1, hk, hd).transpose(1, 2)
+            rot = lambda t: torch.cat((-t[..., hd // 2:], t[..., :hd // 2]), dim=-1)
+            qe, ke = (q4 * cos.unsqueeze(1)) + (rot(q4) * sin.unsqueeze(1)), (k4 * cos.unsqueeze(1)) + (rot(k4) * sin.unsqueeze(1))
+            rk[:, :, pos], rv[:, :, pos] = ke[:, :, 0], v4[:, :, 0]
+            kk, vv = rk.repeat_interleave(hq // hk, dim=1).float(), rv.repeat_interleave(hq // hk, dim=1).float()
+            s = (qe.float() @ kk.transpose(-1, -2)) * scale
+            s = s.masked_fill(~mask, float("-inf"))
+            want = (torch.softmax(s, -1) @ vv).transpose(1, 2).reshape(B, 1, hq * hd)
+            assert int(layer.cumulative_length) == pos + 1
+            assert torch.equal(keys, rk) and torch.equal(vals, rv)                                  # cache written exactly
+            assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
