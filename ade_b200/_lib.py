@@ -10,6 +10,7 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libade_b200.so")
+SHIM_PATH = os.path.join(_HERE, "libade_b200_torch.so")
 
 ADE_OK = 0
 ERRORS = {
@@ -108,6 +109,24 @@ def load() -> ctypes.CDLL:
         getattr(lib, name).restype = ci
     _lib = lib
     return lib
+
+
+_ops = None
+
+
+def ops():
+    """``torch.ops.ade_b200``: the thin torch binding of the two hot entry points (csrc/torch_shim.cpp).  Raises if it
+    has not been built; there is nothing to fall back to."""
+    global _ops
+    if _ops is None:
+        import torch
+
+        load()                                  # the binding links against the kernel library
+        if not os.path.exists(SHIM_PATH):
+            raise AdeKernelError(f"{SHIM_PATH} is missing: build it with `python -m ade_b200.build`")
+        torch.ops.load_library(SHIM_PATH)
+        _ops = torch.ops.ade_b200
+    return _ops
 
 
 def set_option(option: int, value: int) -> None:

@@ -267,18 +267,32 @@ def factored_forward(x: torch.Tensor, p4: dict, weight: torch.Tensor | None = No
         _check_x(y_dense, M, "y_dense")
         if y_dense.shape[0] != T:
             raise ValueError("y_dense and x disagree on T")
-    out = torch.empty((T, M), dtype=torch.bfloat16, device=x.device)
     with _on_device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
-        nbytes = lib.ade_b200_factored_scratch_bytes(T, r)
-        scratch = _scratch_for(x.device, stream, T, r, nbytes)
-        rc = lib.ade_b200_factored(
-            ctypes.byref(_cdelta(p4)), x.data_ptr(),
-            None if y_dense is None else y_dense.data_ptr(),
-            None if weight is None else weight.data_ptr(),
-            out.data_ptr(), scratch.data_ptr(), scratch.numel(), T, stream)
-    _lib.check(rc, "ade_b200_factored")
-    return out
+        scratch = _scratch_for(x.device, stream, T, r, lib.ade_b200_factored_scratch_bytes(T, r))
+        # through the torch binding: it allocates the output, takes torch's current stream and calls ade_b200_factored
+        try:
+            return _lib.ops().factored(x, weight, y_dense, p4["uq"], p4["vq"], p4["vt"], p4["us"], p4["uz"], p4["vs"], p4["vz"],
+                                       M, N, r, _flat_blocks(p4), scratch)
+        except RuntimeError as e:
+            raise _kernel_error(e) from None
+
+
+def _kernel_error(e: RuntimeError) -> Exception:
+    """A status the C ABI returned comes back from the binding as a RuntimeError; give it the library's own type."""
+    msg = str(e).split("\n")[0]
+    return _lib.AdeKernelError(msg) if msg.startswith("ade_b200_") else e
+
+
+def _flat_blocks(p4: dict):
+    """Block structure of a fused group's U^ as the flat (row, group, row, group, ...) list the binding takes."""
+    fb = p4.get("_flat_blocks")
+    if fb is None:
+        blocks = p4.get("blocks")
+        if blocks and not 2 <= len(blocks) <= _lib.MAX_BLOCKS + 1:
+            raise ValueError("stored form: at most %d blocks" % _lib.MAX_BLOCKS)
+        fb = p4["_flat_blocks"] = [int(v) for pair in (blocks or []) for v in pair]
+    return fb
 
 
 def decode_forward_packed(x, y_dense, p4, group_size=GROUP, split_k=False):
@@ -301,20 +315,14 @@ def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None):
     """
     if group_size != GROUP:
         raise ValueError("the kernels are specialised for group size 128")
-    lib = _lib.load()
     M, N, r = int(p4["M"]), int(p4["N"]), int(p4["r"])
     if not (base.dtype == torch.bfloat16 and base.is_cuda and tuple(base.shape) == (M, N)):
         raise ValueError(f"base must be a CUDA bfloat16 ({M}, {N}) tensor")
-    base = base.contiguous()
-    out = torch.empty_like(base)
     if dbg_acc is not None and not (dbg_acc.dtype == torch.int32 and dbg_acc.is_contiguous()
                                     and tuple(dbg_acc.shape) == (r // GROUP, M, N)):
         raise ValueError("dbg_acc must be a contiguous int32 (ng, d_o, d_i) tensor")
     with _on_device(base.device):
-        rc = lib.ade_b200_recon(
-            ctypes.byref(_cdelta(p4)), base.data_ptr(), out.data_ptr(),
-            None if dbg_acc is None else dbg_acc.data_ptr(),
-            None if status is None else status.data_ptr(),
-            torch.cuda.current_stream().cuda_stream)
-    _lib.check(rc, "ade_b200_recon")
-    return out
+        try:
+            return _lib.ops().recon(base, p4["uq"], p4["vq"], p4["vt"], p4["us"], p4["uz"], p4["vs"], p4["vz"], M, N, r, dbg_acc, status)
+        except RuntimeError as e:
+            raise _kernel_error(e) from None

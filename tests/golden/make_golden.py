@@ -60,7 +60,7 @@ def synth(M, N, r, T, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds src/)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     import adaptation

@@ -110,6 +110,15 @@ def test_library_exports_every_declared_symbol():
     assert lib.ade_b200_factored_scratch_bytes(0, 256) == 0
 
 
+def test_torch_binding_loads_and_registers_its_operators():
+    """The thin torch binding (libade_b200_torch.so) loads without a GPU and registers the two hot entry points."""
+    ops = _lib.ops()
+    assert str(ops.factored.default._schema).startswith("ade_b200::factored(Tensor x, Tensor? weight, Tensor? y_dense, Tensor uq")
+    assert "Tensor? dbg_acc, Tensor? status) -> Tensor" in str(ops.recon.default._schema)
+    with pytest.raises((RuntimeError, NotImplementedError)):           # CPU tensors: no CPU kernel is registered
+        ops.recon(torch.zeros(128, 128, dtype=torch.bfloat16), *[torch.zeros(1, dtype=torch.uint8)] * 7, 128, 128, 128, None, None)
+
+
 def test_status_tables_follow_the_header():
     """The Python tables of return codes and device status codes name exactly what the header defines."""
     header = open(os.path.join(ROOT, "include", "ade_b200.h")).read()
