@@ -22,10 +22,35 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                        __nv_bfloat16* __restrict__ out, int H, long long x_stride, float eps) {
     __shared__ float part[8];
     const __nv_bfloat16* xr = x + static_cast<size_t>(blockIdx.x) * x_stride;
+    __nv_bfloat16* orow = out + static_cast<size_t>(blockIdx.x) * H;
+    // 16-byte pieces (8 values), up to four per thread kept in registers between the two passes (rows up to 8192 wide);
+    // rows that are wider, not a multiple of 8 or not 16-byte aligned take the element-wise loops
+    const bool vec = (H & 7) == 0 && H <= 8192 && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    const int nvec = H >> 3;
+    uint4 xv[4];
     float s = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = __bfloat162float(xr[i]);
-        s += v * v;
+    if (vec) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + k * 256;
+            xv[k] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < nvec) xv[k] = reinterpret_cast<const uint4*>(xr)[i];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t ww[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float a = __uint_as_float(ww[e] << 16), c = __uint_as_float(ww[e] & 0xFFFF0000u);
+                s += a * a;
+                s += c * c;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = __bfloat162float(xr[i]);
+            s += v * v;
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
@@ -35,10 +60,29 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += part[i];
     const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
-    __nv_bfloat16* orow = out + static_cast<size_t>(blockIdx.x) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float n = bf16r(__bfloat162float(xr[i]) * inv);
-        orow[i] = __float2bfloat16_rn(__bfloat162float(w[i]) * n);
+    if (vec) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + k * 256;
+            if (i < nvec) {
+                const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
+                const uint32_t xx[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                uint32_t oo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float n0 = bf16r(__uint_as_float(xx[e] << 16) * inv), n1 = bf16r(__uint_as_float(xx[e] & 0xFFFF0000u) * inv);
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(ww[e] << 16) * n0, __uint_as_float(ww[e] & 0xFFFF0000u) * n1);
+                    oo[e] = *reinterpret_cast<const uint32_t*>(&o);
+                }
+                reinterpret_cast<uint4*>(orow)[i] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float n = bf16r(__bfloat162float(xr[i]) * inv);
+            orow[i] = __float2bfloat16_rn(__bfloat162float(w[i]) * n);
+        }
     }
 }
 
@@ -186,24 +230,76 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* _
     __syncthreads();
     sum = red[0] + red[1] + red[2] + red[3];
     __syncthreads();
-    // weighted sum of v: warp w takes positions w, w + 4, ...; a lane owns hd / 32 consecutive dimensions
-    const int per = hd >> 5;                               // 2, 4 or 8
+    // weighted sum of v: a thread owns 8 consecutive dimensions (one 16-byte piece of a cache row) and every
+    // (128 / (hd / 8))-th position, eight rows in flight at a time; the position lanes are summed through shared memory
+    const int chunks = hd >> 3;                            // 16-byte pieces per row: 4 .. 32
+    const int lanes_p = 128 / chunks;                      // position lanes: 32 .. 4
+    const int c8 = tid % chunks, pl = tid / chunks;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int p = warp; p < hi; p += 4) {
-        const float w = sc[p];
-        if (w == 0.f) continue;
-        if (p == p0) {
-            for (int i = 0; i < per; ++i) acc[i] += w * vn[lane * per + i];
-        } else {
-            const __nv_bfloat16* row = vcb + static_cast<size_t>(p) * hd + lane * per;
-            for (int i = 0; i < per; ++i) acc[i] += w * __bfloat162float(row[i]);
+    auto add_row = [&](const uint4& w, float wt) {
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += wt * __uint_as_float(ww[e] << 16);
+            acc[2 * e + 1] += wt * __uint_as_float(ww[e] & 0xFFFF0000u);
+        }
+    };
+    if (pl < lanes_p) {
+        const uint4* vrow = reinterpret_cast<const uint4*>(vcb) + c8;
+        const int stride = chunks;                         // uint4 per row
+        int p = pl;
+        for (; p + 7 * lanes_p < hi; p += 8 * lanes_p) {
+            uint4 w4[8];
+            float wt[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int pp = p + u * lanes_p;
+                wt[u] = pp == p0 ? 0.f : sc[pp];
+                w4[u] = vrow[static_cast<size_t>(pp) * stride];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) add_row(w4[u], wt[u]);
+        }
+        for (; p + 3 * lanes_p < hi; p += 4 * lanes_p) {
+            uint4 w4[4];
+            float wt[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int pp = p + u * lanes_p;
+                wt[u] = pp == p0 ? 0.f : sc[pp];           // the new token's row is added from registers below
+                w4[u] = vrow[static_cast<size_t>(pp) * stride];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) add_row(w4[u], wt[u]);
+        }
+        for (; p < hi; p += lanes_p)
+            if (p != p0) add_row(vrow[static_cast<size_t>(p) * stride], sc[p]);
+        if (pl == 0 && p0 >= 0 && p0 < hi) {
+            const float wt = sc[p0];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += wt * vn[c8 * 8 + i];
         }
     }
-    for (int i = 0; i < per; ++i) red[warp * hd + lane * per + i] = acc[i];
-    __syncthreads();
-    for (int d = tid; d < hd; d += 128) {
-        const float o = (red[d] + red[hd + d] + red[2 * hd + d] + red[3 * hd + d]) / sum;
-        out[(static_cast<size_t>(b) * hq + h) * hd + d] = __float2bfloat16_rn(o);
+    __syncthreads();                                       // sc is no longer read: reuse it with red for the lane sums
+    // the position lanes are folded into lane 0 four at a time through red ([4][hd] floats)
+    for (int round = 0; round < lanes_p; round += 4) {
+        if (pl >= round && pl < round + 4 && pl < lanes_p)
+            for (int i = 0; i < 8; ++i) red[(pl - round) * hd + c8 * 8 + i] = acc[i];
+        __syncthreads();
+        if (pl == 0) {
+            const int n = min(4, lanes_p - round);
+            for (int i = 0; i < 8; ++i) {
+                float t = 0.f;
+                for (int j = (round == 0 ? 1 : 0); j < n; ++j) t += red[j * hd + c8 * 8 + i];
+                acc[i] += t;
+            }
+        }
+        __syncthreads();
+    }
+    if (pl == 0) {
+        __nv_bfloat16* o = out + (static_cast<size_t>(b) * hq + h) * hd + c8 * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(acc[i] / sum);
     }
 }
 
