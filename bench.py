@@ -15,6 +15,8 @@ The printed JSON line carries, next to the device-resident throughput (`value`):
                  gate / down (r = 512) at T = 1, each call replayed from a CUDA graph over rotated instances;
   decode         config 2: random-init Llama-2-7B architecture (32 layers, 224 delta modules, ranks drawn for
                  alpha = 1/16), batch 1, 64-token prompt, 128 greedy tokens, decode step replayed from a CUDA graph;
+  prefill_decode_13b   config 3: Llama-2-13B architecture (40 layers, 280 delta modules), batch 8, 512-token prompts run
+                 as one reconstructed-path prefill (T = 4096), then 64 greedy steps on the factored path (T = 8);
   gpu_reference  the reference's own Blackwell route for this step restated in torch (torch._int_mm per group,
                  float32 rescale, base add, F.linear: src/quantization.py:303-316, src/serving.py:84-92), timed
                  on the same three modules;
@@ -267,22 +269,24 @@ def decode_section(torch, dev, peak, arch="7b", batch=1, prompt=64, new=128, see
                        (mlp.down_proj, xi)):
             calls.append(lambda m=m, xin=xin: m(xin))
     linear_ms = time_graph_calls(torch, calls, reps=5) * len(calls) / 1e3
-    # bytes the decode step has to stream once per token: every linear weight, the delta (codes, scales, zero-points,
-    # with V^T counted once), the output head; the KV cache of <= 192 positions is below 0.1 GB and left out
+    # bytes the decode step has to stream once per step: every linear weight, the delta (codes, scales, zero-points,
+    # with V^T counted once), the output head, and the KV cache of every sequence at its mean length over the run
     h, inter, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
     shapes = [(h, h)] * 4 + [(inter, h)] * 2 + [(h, inter)]
     wbytes = 2.0 * sum(a * b for a, b in shapes) * L
     dbytes = sum((a + b) * r / 2.0 + 2.5 * (a + b) * (r // 128) for (a, b), r in zip(shapes * L, ranks))
     head = 2.0 * cfg.vocab_size * h
-    total = wbytes + dbytes + head
+    kv = 2.0 * 2.0 * batch * L * h * (prompt + new / 2.0)
+    total = wbytes + dbytes + head + kv
     ceiling = peak * 1e9 / total * batch
     res = {
         "config": f"llama-{arch} architecture, random init, {len(ranks)} delta modules (alpha=1/16 ranks, mean {sum(ranks) / len(ranks):.0f}), "
-                  f"batch {batch}, prompt {prompt}, {new} greedy tokens, factored path, decode step replayed from a CUDA graph",
-        "layers": L, "tokens_per_s": batch / per_token, "ms_per_token": per_token * 1e3,
+                  f"batch {batch}, prompt {prompt} ({'reconstructed' if batch * prompt > 128 else 'factored'}-path prefill), {new} greedy tokens on the "
+                  f"factored path, decode step replayed from a CUDA graph",
+        "layers": L, "tokens_per_s": batch / per_token, "ms_per_step": per_token * 1e3, "tokens_per_step": batch,
         "eager_tokens_per_s": batch / eager_per_token, "eager_us_per_module_call": eager_per_token * 1e6 / len(ranks),
-        "delta_modules_ms_per_token": linear_ms, "rest_of_model_ms_per_token": per_token * 1e3 - linear_ms,
-        "prefill_ms": t_prefill * 1e3, "bytes_per_token": total, "ceiling_tokens_per_s": ceiling,
+        "delta_modules_ms_per_step": linear_ms, "rest_of_model_ms_per_step": per_token * 1e3 - linear_ms,
+        "prefill_ms": t_prefill * 1e3, "bytes_per_step": total, "ceiling_tokens_per_s": ceiling,
         "frac_of_ceiling": batch / per_token / ceiling,
         "tokens_equal_eager": bool((out[:, :prompt + n_eager + 1] == eager).all()), "fused_groups": groups, "model_build_s": build_s,
     }
@@ -581,7 +585,7 @@ def run_ade(args):
         i8 = int8_peak(torch, dev)
     del mods, xs_dev, x_stage
     torch.cuda.empty_cache()
-    sharded = multi = None
+    sharded = multi = decode13 = None
     if not args.skip_model:
         if world > 1:
             sharded = sharded_recon_section(torch, dist, dev, rank, world, barrier)
@@ -589,6 +593,7 @@ def run_ade(args):
         else:
             sharded = sharded_recon_section(torch, dist, dev, 0, 1, barrier)
             decode = decode_section(torch, dev, peak)
+            decode13 = decode_section(torch, dev, peak, "13b", batch=8, prompt=512, new=64, seed=3)
     kernels.check_factored_status(dev)
 
     if world > 1:
@@ -624,7 +629,7 @@ def run_ade(args):
             "cpu_baseline": {"value": cpu_tops, "unit": UNIT, "cores": cpu_threads, "blas_threads": blas, "kind": "port",
                              "sample": f"{cpu_rows} of 11008 rows of gate_proj: reconstruct + base add + x W'^T, median of 5, {cpu_sec:.2f} s per pass"},
             "clocks": sampler.summary(t_wall0, t_wall2),
-            "factored": factored, "decode": decode, "gpu_reference": gpu_ref, "int8_peak_measured": i8,
+            "factored": factored, "decode": decode, "prefill_decode_13b": decode13, "gpu_reference": gpu_ref, "int8_peak_measured": i8,
             "sharded_recon": sharded, "multi_delta_decode": multi,
             "wall_s_timed": t_wall1 - t_wall0,
         }
