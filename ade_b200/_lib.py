@@ -44,7 +44,7 @@ EXPORTS = (
     "ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_compress_rows",
     "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored",
     "ade_b200_factored_static", "ade_b200_factored_static_status", "ade_b200_recon", "ade_b200_set_option",
-    "ade_b200_rmsnorm", "ade_b200_rope", "ade_b200_silu_mul", "ade_b200_attn_decode",
+    "ade_b200_rmsnorm", "ade_b200_add_rmsnorm", "ade_b200_rope", "ade_b200_silu_mul", "ade_b200_attn_decode",
 )
 
 
@@ -100,8 +100,9 @@ def load() -> ctypes.CDLL:
     lib.ade_b200_rmsnorm.argtypes = [vp, vp, vp, ci, ci, ll, ctypes.c_float, vp]
     lib.ade_b200_rope.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll, ll, ll, vp]
     lib.ade_b200_silu_mul.argtypes = [vp, vp, vp, ci, ci, ll, ll, vp]
-    lib.ade_b200_attn_decode.argtypes = [vp] * 10 + [ci] * 5 + [ll] * 5 + [ctypes.c_float, vp]
-    for name in ("ade_b200_rmsnorm", "ade_b200_rope", "ade_b200_silu_mul", "ade_b200_attn_decode"):
+    lib.ade_b200_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, ci, ci, ll, ll, ctypes.c_float, vp]
+    lib.ade_b200_attn_decode.argtypes = [vp] * 11 + [ci] * 5 + [ll] * 5 + [ctypes.c_float, vp]
+    for name in ("ade_b200_rmsnorm", "ade_b200_add_rmsnorm", "ade_b200_rope", "ade_b200_silu_mul", "ade_b200_attn_decode"):
         getattr(lib, name).restype = ci
     lib.ade_b200_set_option.argtypes = [ci, ctypes.c_longlong]
     lib.ade_b200_set_option.restype = ci

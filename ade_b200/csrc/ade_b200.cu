@@ -27,7 +27,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxRowsCap = 320;    // rows of one CTA's slice that fit the shared-memory y buffer (T = 128)
-constexpr size_t kFifoMinStream = 400 * 1024;   // bytes of W_b per CTA from which the FIFO pays off at 9-16 tokens
+#ifndef ADE_FIFO_MIN
+#define ADE_FIFO_MIN (400 * 1024)
+#endif
+constexpr size_t kFifoMinStream = ADE_FIFO_MIN;   // bytes of W_b per CTA from which the FIFO pays off at 9-16 tokens
 constexpr int kMaxSmem = 232448;     // opt-in dynamic shared memory per CTA on sm_100
 struct DeviceInfo {
     int ready = 0;      // 1 = usable, -1 = wrong architecture
@@ -178,6 +181,13 @@ int launch_grid(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t 
     cfg.attrs = attr;
     cfg.numAttrs = g_cooperative ? 1 : 0;
     return cuda_ok(cudaLaunchKernelEx(&cfg, kernel, p)) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+// Launch of one of the small decode-step kernels.
+template <class Kernel, class... Args>
+int launch_small(Kernel kernel, int grid, int threads, size_t smem, void* stream, Args... args) {
+    kernel<<<grid, threads, smem, static_cast<cudaStream_t>(stream)>>>(args...);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
 }
 
 template <int NT, bool FUSE>
@@ -468,9 +478,18 @@ int ade_b200_compress_rows(const float* x, const float* sqrt_s, uint8_t* codes, 
 int ade_b200_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, long long x_row_stride, float eps, void* stream) {
     if (!x || !weight || !out) return ADE_ERR_NULL;
     if (rows < 1 || H < 1 || x_row_stride < H) return ADE_ERR_SHAPE;
-    ade::rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), H, x_row_stride, eps);
-    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    return launch_small(ade::rmsnorm_kernel, rows, 256, 0, stream, static_cast<const __nv_bfloat16*>(x),
+                        static_cast<const __nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(weight),
+                        static_cast<__nv_bfloat16*>(nullptr), static_cast<__nv_bfloat16*>(out), H, x_row_stride, 0LL, eps);
+}
+
+int ade_b200_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int rows, int H,
+                         long long x_row_stride, long long residual_row_stride, float eps, void* stream) {
+    if (!x || !residual || !weight || !sum_out || !out) return ADE_ERR_NULL;
+    if (rows < 1 || H < 1 || x_row_stride < H || residual_row_stride < H) return ADE_ERR_SHAPE;
+    return launch_small(ade::rmsnorm_kernel, rows, 256, 0, stream, static_cast<const __nv_bfloat16*>(x),
+                        static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(weight),
+                        static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(out), H, x_row_stride, residual_row_stride, eps);
 }
 
 int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out, int B, int T, int q_heads,
@@ -479,11 +498,9 @@ int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* s
     if (B < 1 || T < 1 || q_heads < 1 || k_heads < 1 || head_dim < 2 || (head_dim & 1)) return ADE_ERR_SHAPE;
     const long long total = static_cast<long long>(B) * T * (q_heads + k_heads) * head_dim;
     const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    ade::rope_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(cos_t),
-        static_cast<const __nv_bfloat16*>(sin_t), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), B, T, q_heads,
-        k_heads, head_dim, q_row_stride, k_row_stride, cs_batch_stride);
-    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    return launch_small(ade::rope_kernel, blocks, 256, 0, stream, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                        static_cast<const __nv_bfloat16*>(cos_t), static_cast<const __nv_bfloat16*>(sin_t), static_cast<__nv_bfloat16*>(q_out),
+                        static_cast<__nv_bfloat16*>(k_out), B, T, q_heads, k_heads, head_dim, q_row_stride, k_row_stride, cs_batch_stride);
 }
 
 int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, long long gate_row_stride, long long up_row_stride,
@@ -492,14 +509,12 @@ int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int
     if (rows < 1 || cols < 1 || gate_row_stride < cols || up_row_stride < cols) return ADE_ERR_SHAPE;
     const long long total = static_cast<long long>(rows) * cols;
     const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    ade::silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), rows, cols,
-        gate_row_stride, up_row_stride);
-    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    return launch_small(ade::silu_mul_kernel, blocks, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+                        static_cast<__nv_bfloat16*>(out), rows, cols, gate_row_stride, up_row_stride);
 }
 
 int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void* cos_t, const void* sin_t, const void* mask, void* k_cache,
-                         void* v_cache, const long long* pos, void* out, int B, int q_heads, int k_heads, int head_dim, int cache_len,
+                         void* v_cache, long long* pos, unsigned int* ticket, void* out, int B, int q_heads, int k_heads, int head_dim, int cache_len,
                          long long q_row_stride, long long k_row_stride, long long v_row_stride, long long cs_batch_stride,
                          long long mask_row_stride, float scale, void* stream) {
     if (!q || !k || !v || !cos_t || !sin_t || !k_cache || !v_cache || !pos || !out) return ADE_ERR_NULL;
@@ -508,12 +523,11 @@ int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void
     if (!aligned16(k_cache) || !aligned16(v_cache)) return ADE_ERR_ALIGN;
     const size_t smem = (static_cast<size_t>(7) * head_dim + cache_len) * sizeof(float);
     if (smem > 48 * 1024) return ADE_ERR_SHAPE;                           // cache lengths up to about 10 000 positions
-    ade::attn_decode_kernel<<<B * q_heads, 128, smem, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
-        static_cast<const __nv_bfloat16*>(cos_t), static_cast<const __nv_bfloat16*>(sin_t), static_cast<const bool*>(mask),
-        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), pos, static_cast<__nv_bfloat16*>(out), q_heads, k_heads,
-        head_dim, cache_len, q_row_stride, k_row_stride, v_row_stride, cs_batch_stride, mask_row_stride, scale);
-    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+    return launch_small(ade::attn_decode_kernel, B * q_heads, 128, smem, stream, static_cast<const __nv_bfloat16*>(q),
+                        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), static_cast<const __nv_bfloat16*>(cos_t),
+                        static_cast<const __nv_bfloat16*>(sin_t), static_cast<const bool*>(mask), static_cast<__nv_bfloat16*>(k_cache),
+                        static_cast<__nv_bfloat16*>(v_cache), pos, ticket, static_cast<__nv_bfloat16*>(out), q_heads, k_heads, head_dim, cache_len,
+                        q_row_stride, k_row_stride, v_row_stride, cs_batch_stride, mask_row_stride, scale);
 }
 
 int ade_b200_factored_static_status(int* dst, int clear, void* stream) {

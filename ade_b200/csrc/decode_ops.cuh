@@ -18,14 +18,21 @@ __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__floa
 
 // out[t][:] = w * bf16(x[t][:] * rsqrt(mean(x[t][:]^2) + eps)): float32 statistics, the normalised value rounded to
 // bfloat16 before the (bfloat16) multiplication by the weight, as LlamaRMSNorm.forward does.  One CTA per row.
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                                                       __nv_bfloat16* __restrict__ out, int H, long long x_stride, float eps) {
+// With `res` the row normalised is s = bf16(x + res) (the residual connection, rounded as torch rounds the sum of two
+// bfloat16 tensors) and s is written to `sum_out` as well: residual add and the following RMSNorm in one launch.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ sum_out,
+                                                       __nv_bfloat16* __restrict__ out, int H, long long x_stride, long long res_stride,
+                                                       float eps) {
     __shared__ float part[8];
     const __nv_bfloat16* xr = x + static_cast<size_t>(blockIdx.x) * x_stride;
+    const __nv_bfloat16* rr = res ? res + static_cast<size_t>(blockIdx.x) * res_stride : nullptr;
+    __nv_bfloat16* srow = sum_out ? sum_out + static_cast<size_t>(blockIdx.x) * H : nullptr;
     __nv_bfloat16* orow = out + static_cast<size_t>(blockIdx.x) * H;
     // 16-byte pieces (8 values), up to four per thread kept in registers between the two passes (rows up to 8192 wide);
     // rows that are wider, not a multiple of 8 or not 16-byte aligned take the element-wise loops
-    const bool vec = (H & 7) == 0 && H <= 8192 && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    const bool vec = (H & 7) == 0 && H <= 8192 &&
+                     ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(rr)) & 15) == 0;
     const int nvec = H >> 3;
     uint4 xv[4];
     float s = 0.f;
@@ -34,7 +41,22 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
         for (int k = 0; k < 4; ++k) {
             const int i = threadIdx.x + k * 256;
             xv[k] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < nvec) xv[k] = reinterpret_cast<const uint4*>(xr)[i];
+            if (i < nvec) {
+                xv[k] = reinterpret_cast<const uint4*>(xr)[i];
+                if (rr) {
+                    const uint4 rv = reinterpret_cast<const uint4*>(rr)[i];
+                    uint32_t xx[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+                    const uint32_t r4[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(xx[e] << 16) + __uint_as_float(r4[e] << 16),
+                                                                        __uint_as_float(xx[e] & 0xFFFF0000u) + __uint_as_float(r4[e] & 0xFFFF0000u));
+                        xx[e] = *reinterpret_cast<const uint32_t*>(&o);
+                    }
+                    xv[k] = make_uint4(xx[0], xx[1], xx[2], xx[3]);
+                    reinterpret_cast<uint4*>(srow)[i] = xv[k];
+                }
+            }
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -48,7 +70,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
         }
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = __bfloat162float(xr[i]);
+            float v = __bfloat162float(xr[i]);
+            if (rr) {
+                v = bf16r(v + __bfloat162float(rr[i]));
+                srow[i] = __float2bfloat16_rn(v);
+            }
             s += v * v;
         }
     }
@@ -79,8 +105,9 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
             }
         }
     } else {
+        const __nv_bfloat16* src = rr ? srow : xr;           // the sum was written above by this very thread
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float n = bf16r(__bfloat162float(xr[i]) * inv);
+            const float n = bf16r(__bfloat162float(src[i]) * inv);
             orow[i] = __float2bfloat16_rn(__bfloat162float(w[i]) * n);
         }
     }
@@ -138,12 +165,14 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ g, const __nv_
 //   nullptr = attend to positions 0 .. *pos; out [B][hq*hd] contiguous.
 // The new k (rotated, rounded to bfloat16 as the cache stores it) and v are used from registers for position *pos, so
 // no CTA reads what another one writes in the same launch; the CTA of the first query head of every KV group writes
-// them to the cache.  Scores, softmax and the weighted sum are float32.
+// them to the cache.  Scores, softmax and the weighted sum are float32.  With `ticket` (a zero-initialised counter of
+// its own per cache layer) the launch also advances *pos by one once every CTA has read it.
 __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                                                            const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ cs,
                                                            const __nv_bfloat16* __restrict__ sn, const bool* __restrict__ mask,
                                                            __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
-                                                           const long long* __restrict__ pos, __nv_bfloat16* __restrict__ out, int hq, int hk,
+                                                           long long* __restrict__ pos, unsigned int* __restrict__ ticket,
+                                                           __nv_bfloat16* __restrict__ out, int hq, int hk,
                                                            int hd, int L, long long q_stride, long long k_stride, long long v_stride,
                                                            long long cs_batch_stride, long long mask_stride, float scale) {
     extern __shared__ float at_smem[];
@@ -156,6 +185,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* _
     const int group = hq / hk, kvh = h / group;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int p0 = static_cast<int>(*pos);
+    if (ticket != nullptr) {
+        // every CTA has read the position by the time the last ticket is drawn: that CTA advances it for the next
+        // step and re-arms the counter (nobody reads *pos again in this launch)
+        __syncthreads();
+        if (tid == 0 && atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            *pos = p0 + 1;
+            *ticket = 0u;
+        }
+    }
     const int half = hd >> 1;
     const __nv_bfloat16* qr = q + static_cast<size_t>(b) * q_stride + h * hd;
     const __nv_bfloat16* kr = k + static_cast<size_t>(b) * k_stride + kvh * hd;

@@ -250,14 +250,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                         for (int kk = 0; kk < 4; ++kk) {
                             const int k = h4 * 4 + kk;
                             const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(vc[2 * k]), __uint_as_float(vc[2 * k + 1])), uu, cc);
-#ifdef RS_HYBRID
-                            float t0, t1, a0, a1;
-                            f2_unpack(f2_mul(x2, vs2[kk]), t0, t1);
-                            f2_unpack(acc[ch * 8 + k], a0, a1);
-                            acc[ch * 8 + k] = f2_pack(__fadd_rn(a0, t0), __fadd_rn(a1, t1));
-#else
                             acc[ch * 8 + k] = f2_fma(f2_mul(x2, vs2[kk]), one2, acc[ch * 8 + k]);
-#endif
                         }
                     }
                     if (DBG && live) {

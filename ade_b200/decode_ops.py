@@ -41,6 +41,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out.view(x.shape)
 
 
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """(residual + x, LlamaRMSNorm(residual + x)) in one launch: the residual connection of a decoder layer and the
+    normalisation that follows it.  Both inputs bfloat16 CUDA with a contiguous last dimension."""
+    H = x.shape[-1]
+    x2, r2 = x.reshape(-1, H), residual.reshape(-1, H)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if r2.stride(1) != 1:
+        r2 = r2.contiguous()
+    total = torch.empty((x2.shape[0], H), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty_like(total)
+    _lib.check(_lib.load().ade_b200_add_rmsnorm(x2.data_ptr(), r2.data_ptr(), weight.data_ptr(), total.data_ptr(), out.data_ptr(), x2.shape[0], H,
+                                                x2.stride(0), r2.stride(0), float(eps), _stream()), "ade_b200_add_rmsnorm")
+    return total.view(x.shape), out.view(x.shape)
+
+
 def rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
     """apply_rotary_pos_emb for q (B, heads, T, hd) and k given as transposed views of (B, T, heads, hd) projections;
     returns contiguous (B, heads, T, hd) tensors."""
@@ -70,18 +86,20 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 def attn_decode(q, k, v, cos, sin, mask, layer, scale: float) -> torch.Tensor:
     """Single-token attention step on a static cache layer: q (B, 1, hq*hd), k / v (B, 1, hk*hd) straight from the
     projections, cos / sin (B or 1, 1, hd), mask None or bool (B, 1, 1, L).  Writes k, v into the layer's cache at its
-    running position, advances that position, returns (B, 1, hq*hd)."""
+    running position, advances that position (inside the same launch), returns (B, 1, hq*hd)."""
     B = q.shape[0]
     hk, L, hd = layer.keys.shape[1], layer.keys.shape[2], layer.keys.shape[3]
     hq = q.shape[-1] // hd
     out = torch.empty((B, 1, hq * hd), dtype=torch.bfloat16, device=q.device)
     row = lambda t: t.stride(0) if B > 1 else t.shape[-1]
+    ticket = getattr(layer, "_ade_ticket", None)           # counter through which the launch advances the position itself
+    if ticket is None or ticket.device != q.device:
+        ticket = layer._ade_ticket = torch.zeros(1, dtype=torch.int32, device=q.device)
     _lib.check(_lib.load().ade_b200_attn_decode(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), None if mask is None else mask.data_ptr(),
-        layer.keys.data_ptr(), layer.values.data_ptr(), layer.cumulative_length.data_ptr(), out.data_ptr(), B, hq, hk, hd, L,
+        layer.keys.data_ptr(), layer.values.data_ptr(), layer.cumulative_length.data_ptr(), ticket.data_ptr(), out.data_ptr(), B, hq, hk, hd, L,
         row(q), row(k), row(v), 0 if cos.shape[0] == 1 else hd, 0 if mask is None else mask.stride(0), float(scale), _stream()),
         "ade_b200_attn_decode")
-    layer.cumulative_length.add_(1)
     return out
 
 
@@ -150,7 +168,14 @@ def enable_fused_decode_ops(model) -> int:
         elif isinstance(mod, ml.LlamaRMSNorm) and not hasattr(mod, "_ade_orig_forward"):
             mod._ade_orig_forward = mod.forward
 
+            mod._ade_pre = None                   # (input tensor, its normalisation) left by the layer in front, see below
+
             def norm_forward(x, mod=mod):
+                pre = mod._ade_pre
+                if pre is not None:
+                    mod._ade_pre = None
+                    if x is pre[0]:
+                        return pre[1]
                 if _rows_ok(x, x.numel() // x.shape[-1]) and x.stride(-1) == 1 and mod.weight.dtype == torch.bfloat16:
                     return rmsnorm(x, mod.weight, mod.variance_epsilon)
                 return mod._ade_orig_forward(x)
@@ -170,5 +195,40 @@ def enable_fused_decode_ops(model) -> int:
                 return mod._ade_orig_forward(x)
 
             mod.forward = mlp_forward
+            n += 1
+    # Residual connections: a decoder layer adds the attention output and the MLP output to its input, each time right in
+    # front of an RMSNorm (its own post-attention norm; the next layer's input norm, or the model's final norm).  A
+    # patched layer does add + norm in one launch each and leaves the second normalisation with the norm module that is
+    # about to be asked for it, which recognises the tensor by identity.
+    for lm in model.modules():
+        if not isinstance(lm, ml.LlamaModel):
+            continue
+        layers = list(lm.layers[: lm.config.num_hidden_layers])
+        for i, layer in enumerate(layers):
+            if hasattr(layer, "_ade_orig_forward") or not isinstance(layer, ml.LlamaDecoderLayer):
+                continue
+            nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else lm.norm
+            if not all(hasattr(nm, "_ade_pre") for nm in (layer.input_layernorm, layer.post_attention_layernorm, nxt)):
+                continue
+            layer._ade_orig_forward = layer.forward
+
+            def layer_forward(hidden_states, attention_mask=None, position_ids=None, past_key_values=None, use_cache=False,
+                              position_embeddings=None, layer=layer, nxt=nxt, **kw):
+                post = layer.post_attention_layernorm
+                if not (_rows_ok(hidden_states, hidden_states.numel() // hidden_states.shape[-1]) and hidden_states.is_contiguous()
+                        and post.weight.dtype == torch.bfloat16 and nxt.weight.dtype == torch.bfloat16 and not layer.training):
+                    return layer._ade_orig_forward(hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+                                                   past_key_values=past_key_values, use_cache=use_cache,
+                                                   position_embeddings=position_embeddings, **kw)
+                h = layer.input_layernorm(hidden_states)
+                a, _ = layer.self_attn(hidden_states=h, attention_mask=attention_mask, position_ids=position_ids,
+                                       past_key_values=past_key_values, use_cache=use_cache, position_embeddings=position_embeddings, **kw)
+                s1, h2 = add_rmsnorm(a, hidden_states, post.weight, post.variance_epsilon)
+                m = layer.mlp(h2)
+                s2, h3 = add_rmsnorm(m, s1, nxt.weight, nxt.variance_epsilon)
+                nxt._ade_pre = (s2, h3)
+                return s2
+
+            layer.forward = layer_forward
             n += 1
     return n

@@ -224,6 +224,7 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
  * more than the delta application they surround.  Same arithmetic and the same bfloat16 roundings as the torch
  * operations they stand in for; all tensors bfloat16, strides in elements.
  *   ade_b200_rmsnorm   out[t][:] = weight * bf16(x[t][:] * rsqrt(mean(x[t][:]^2) + eps)), float32 statistics.
+ *   ade_b200_add_rmsnorm  the residual connection and the RMSNorm behind it: sum_out = bf16(x + residual), out = rmsnorm(sum_out).
  *   ade_b200_rope      q [B][T][q_heads][head_dim] and k [B][T][k_heads][head_dim], given with their row strides (the
  *                      projections may be column slices of one fused output), rotated with cos / sin [B or 1][T][head_dim]
  *                      (cs_batch_stride = T * head_dim, or 0 for one shared table) into q_out [B][q_heads][T][head_dim]
@@ -234,16 +235,20 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
  *                      contiguous) at position *pos (device int64), and softmax(q K^T scale) V over the positions that
  *                      mask (bool [B][cache_len], true = attend, includes *pos; NULL = positions 0..*pos) allows, written to
  *                      out [B][q_heads*head_dim].  Scores and sums in float32.  q_heads % k_heads == 0, head_dim a multiple
- *                      of 32 up to 256, (7 head_dim + cache_len) floats of shared memory <= 48 KB.  *pos is not advanced.
+ *                      of 32 up to 256, (7 head_dim + cache_len) floats of shared memory <= 48 KB.  With ticket != NULL (a
+ *                      device counter of this cache layer's own, zero before its first use) the launch advances *pos by
+ *                      one after every CTA has read it; with NULL *pos is left to the caller.
  */
 int ade_b200_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, long long x_row_stride, float eps, void* stream);
+int ade_b200_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out, void* out, int rows, int H,
+                         long long x_row_stride, long long residual_row_stride, float eps, void* stream);
 int ade_b200_rope(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out, int B, int T,
                   int q_heads, int k_heads, int head_dim, long long q_row_stride, long long k_row_stride, long long cs_batch_stride,
                   void* stream);
 int ade_b200_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, long long gate_row_stride,
                       long long up_row_stride, void* stream);
 int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void* cos_t, const void* sin_t, const void* mask,
-                         void* k_cache, void* v_cache, const long long* pos, void* out, int B, int q_heads, int k_heads,
+                         void* k_cache, void* v_cache, long long* pos, unsigned int* ticket, void* out, int B, int q_heads, int k_heads,
                          int head_dim, int cache_len, long long q_row_stride, long long k_row_stride, long long v_row_stride,
                          long long cs_batch_stride, long long mask_row_stride, float scale, void* stream);
 

@@ -124,6 +124,17 @@ def test_fused_decode_ops_keep_the_torch_arithmetic():
         want_q, want_k = (q * c1(cos)) + (rot(q) * c1(sin)), (k * c1(cos)) + (rot(k) * c1(sin))
         got_q, got_k = decode_ops.rope(q, k, cos, sin)
         assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
+    for rows, H in [(1, 4096), (8, 5120), (3, 1000)]:       # residual add + norm in one launch (1000: the element-wise path)
+        a = torch.randn(rows, H, generator=g).to(torch.bfloat16).to(DEV)
+        r = (torch.randn(rows, H, generator=g) * 4).to(torch.bfloat16).to(DEV)
+        norm = ml.LlamaRMSNorm(H, eps=1e-5).to(DEV).to(torch.bfloat16)
+        with torch.no_grad():
+            want_sum = r + a
+            want = norm(want_sum)
+        got_sum, got = decode_ops.add_rmsnorm(a, r, norm.weight, norm.variance_epsilon)
+        assert torch.equal(got_sum, want_sum)
+        diff = (got.float() - want.float()).abs()
+        assert float((diff > 0).float().mean()) < 1e-3 and float((diff / want.float().abs().clamp(min=1e-3)).max()) < 1e-2
     for rows, cols in [(1, 11008), (8, 13824)]:
         y = (torch.randn(rows, 2 * cols, generator=g) * 2).to(torch.bfloat16).to(DEV)
         gate, up = y[:, :cols], y[:, cols:]
@@ -152,7 +163,8 @@ def test_fused_decode_ops_in_the_model():
     with torch.no_grad():
         before = model(ids).logits.float()
         tokens_before = GreedyGraphDecoder(model).generate(ids, 12)
-    assert decode_ops.enable_fused_decode_ops(model) == 2 * 2 + 1 + 2 + 2      # two norms per layer, the final norm, two MLPs, two attentions
+    # two norms per layer, the final norm, two MLPs, two attentions, two decoder layers (residual add + norm)
+    assert decode_ops.enable_fused_decode_ops(model) == 2 * 2 + 1 + 2 + 2 + 2
     assert decode_ops.enable_fused_decode_ops(model) == 0                      # idempotent
     with torch.no_grad():
         after = model(ids).logits.float()
@@ -201,6 +213,6 @@ def test_attention_decode_step_against_torch():
             s = (qe.float() @ kk.transpose(-1, -2)) * scale
             s = s.masked_fill(~mask, float("-inf"))
             want = (torch.softmax(s, -1) @ vv).transpose(1, 2).reshape(B, 1, hq * hd)
-            assert int(layer.cumulative_length) == pos + 1
+            assert int(layer.cumulative_length) == pos + 1 and int(layer._ade_ticket) == 0     # advanced by the launch itself
             assert torch.equal(keys, rk) and torch.equal(vals, rv)                                  # cache written exactly
             assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
