@@ -215,7 +215,10 @@ int launch_factored_one(ade::FactoredParams p, int grid, cudaStream_t st) {
         }
     }
     // operands of the first phase-U items are prefetched into shared memory: the drained FIFO, or an area of their own
-    if (p.stages >= 2) {
+    // (not up to 8 tokens: there phase U runs on the side warps, under the stream of W_b, and needs no head start)
+    if (ade::fa_side_u(NT)) {
+        p.upf = 0;
+    } else if (p.stages >= 2) {
         p.upf = ade::FA_UPF;
     } else if (smem + static_cast<size_t>(ade::FA_UPF) * ade::FA_UPF_ITEM <= static_cast<size_t>(kMaxSmem)) {
         p.upf = ade::FA_UPF;

@@ -39,6 +39,11 @@ constexpr int FA_WARPS = 8;
 constexpr int FA_THREADS = FA_WARPS * 32;
 constexpr int FA_SIDE_WARPS = 4;               // extra warps that compute h = V^T x next to the W_b stream (T <= 16)
 __host__ __device__ constexpr bool fa_side(int NT) { return NT <= 2; }
+// Up to 8 tokens the side warps, once their share of h is written, also compute the delta term U^ h of their CTA's rows
+// under the main warps' stream of W_b (measured per call on B200: q_proj T = 1 11.4 -> 10.2 us, gate_proj 25.6 -> 22.7,
+// down_proj 21.1 -> 19.9).  At 9-16 tokens four warps take longer over phase U than the stream lasts (gate_proj T = 16
+// 31.0 -> 34.0 us), so there the main warps do it after their stream, as above 16 tokens.
+__host__ __device__ constexpr bool fa_side_u(int NT) { return NT == 1; }
 __host__ __device__ constexpr int fa_threads(int NT) { return FA_THREADS + (fa_side(NT) ? FA_SIDE_WARPS * 32 : 0); }
 
 // barrier among the 8 main warps only (the side warps never join it)
@@ -111,9 +116,11 @@ __host__ __device__ constexpr int fa_fifo_item(int NT) { return (8 + 2 * NT) * 1
 constexpr int FA_FIFO_MAX = 5;
 
 // without the FIFO; the launch adds stages * fa_fifo_item(NT) in front
+// With side warps (T <= 16) the side team has a reduction buffer of its own ([4][32][33]) and a second row buffer
+// (the delta term U^ h of the CTA's rows, which the side warps compute while the main warps still stream W_b).
 __host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap, int T, int r) {
-    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + (fa_side(NT) ? FA_SIDE_WARPS * 32 * 17 : 0) +
-            static_cast<size_t>(rows_cap) * (8 * NT + 1)) * sizeof(float) +
+    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + (fa_side(NT) ? FA_SIDE_WARPS * 32 * 33 : 0) +
+            static_cast<size_t>(rows_cap) * (8 * NT + 1) * (fa_side(NT) ? 2 : 1)) * sizeof(float) +
            (fa_side(NT) ? fa_side_region(T, r) : 0);
 }
 
@@ -141,11 +148,16 @@ __device__ __forceinline__ void fa_cp_async_wait(int n) {      // at most n of t
     }
 }
 
-// Sum the 8 warps' partial tiles in a fixed order.  acc[mt][nt][4] covers 32 rows x 8*NT tokens;
-// sink(row, token, sum) is called once per element by exactly one thread.
-template <int NT, class Sink>
-__device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (&acc)[2][NT][4], int warp, int gid,
-                                             int tig, Sink sink) {
+// Sum a team's partial tiles in a fixed order (TEAM = 8: the main warps, 4: the side warps).  acc[mt][nt][4] covers
+// 32 rows x 8*NT tokens; sink(row, token, sum) is called once per element by exactly one thread of the team.
+template <int TEAM>
+__device__ __forceinline__ void team_sync() {
+    if (TEAM == FA_WARPS) main_sync(); else side_sync();
+}
+template <int NT, int TEAM, class Sink>
+__device__ __forceinline__ void reduce_tiles_team(float (*red)[32][33], const float (&acc)[2][NT][4], int warp, int gid,
+                                                  int tig, Sink sink) {
+    const int tl = (TEAM == FA_WARPS ? threadIdx.x : threadIdx.x - FA_THREADS);      // index inside the team
 #pragma unroll
     for (int b = 0; b < (NT + 3) / 4; ++b) {
 #pragma unroll
@@ -161,20 +173,25 @@ __device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (
                 }
             }
         }
-        main_sync();
+        team_sync<TEAM>();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e = threadIdx.x + i * FA_THREADS;
+        for (int i = 0; i < 1024 / (TEAM * 32); ++i) {
+            const int e = tl + i * TEAM * 32;
             const int row = e & 31, tok = e >> 5;
             if (tok < 8 * (NT - 4 * b)) {
                 float s = 0.f;
 #pragma unroll
-                for (int w = 0; w < FA_WARPS; ++w) s += red[w][tok][row];
+                for (int w = 0; w < TEAM; ++w) s += red[w][tok][row];
                 sink(row, b * 32 + tok, s);
             }
         }
-        main_sync();
+        team_sync<TEAM>();
     }
+}
+template <int NT, class Sink>
+__device__ __forceinline__ void reduce_tiles(float (*red)[32][33], const float (&acc)[2][NT][4], int warp, int gid,
+                                             int tig, Sink sink) {
+    reduce_tiles_team<NT, FA_WARPS>(red, acc, warp, gid, tig, sink);
 }
 
 template <int NT>
@@ -583,7 +600,7 @@ __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* us
 
 // SPLIT: h has been staged in shared memory (hs, bf16 [T][r + 8]); otherwise it is read from p.h (L2).
 // k: running index of this warp's items over the blocks (the first p.upf were prefetched).
-template <int NT, bool SPLIT>
+template <int NT, bool SPLIT, int TEAM = FA_WARPS>
 __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
                                          const __nv_bfloat16* hs, const uint8_t* ustage, int& k, int warp, int gid, int tig) {
     const int T = p.T, r = p.r;
@@ -592,7 +609,7 @@ __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2
     int g_lo, g_hi;
     fa_group_range(p, blk, min(blk + FA_ROWS, row_end), g_lo, g_hi);
     constexpr int NS = fa_u_split(NT);
-    for (int j = warp; j < 2 * (g_hi - g_lo) * NS; j += FA_WARPS, ++k) {
+    for (int j = warp; j < 2 * (g_hi - g_lo) * NS; j += TEAM, ++k) {
         const int part = j % NS, jj = j / NS;               // token tiles [part * NT / NS, (part + 1) * NT / NS)
         const int mt = jj & 1, g = g_lo + (jj >> 1);
         uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
@@ -678,8 +695,11 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(fsmem);
     constexpr int YS = 8 * NT + 1;                         // padded row stride of the y buffer
     constexpr bool SIDE = fa_side(NT);
-    float* side_red = fsmem + FA_WARPS * 32 * 33;          // [4][32][17]
-    float* ybuf = side_red + (SIDE ? FA_SIDE_WARPS * 32 * 17 : 0);     // [rows_cap][YS]
+    constexpr bool SIDE_U = fa_side_u(NT);                 // the side warps also compute the delta term (phase U)
+    float* side_red = fsmem + FA_WARPS * 32 * 33;          // [4][32][33], the side team's reduction buffer
+    float* ybuf = side_red + (SIDE ? FA_SIDE_WARPS * 32 * 33 : 0);     // [rows_cap][YS] base term of the CTA's rows
+    float* ydel = ybuf + static_cast<size_t>(p.rows_cap) * YS;         // [rows_cap][YS] delta term (side warps only)
+    float* after_rows = ybuf + static_cast<size_t>(p.rows_cap) * YS * (SIDE ? 2 : 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int G = gridDim.x, c = blockIdx.x;
     const int parts = SIDE ? 2 : p.parts;                  // slices of d_i per 16 ranks (side warps: two halves)
@@ -698,13 +718,67 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
             xv_unit<NT, FA_SIDE_WARPS, FIFO>(p, side_red, (u >> 1) * 16, half ? mid : 0, half ? nchunks : mid,
                                        reinterpret_cast<float*>(p.h) + static_cast<size_t>(half) * p.T * p.r,
                                        warp - FA_WARPS, gid, tig,
-                                       FIFO ? reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * (8 * NT + 1))
-                                            : nullptr);                 // staged with the FIFO, from registers without
+                                       FIFO ? reinterpret_cast<uint8_t*>(after_rows) : nullptr);   // staged with the FIFO, from registers without
             ++done;
         }
         // xv_unit ended with a barrier of the side warps; the release orders their stores of h before the count.
         // One fire-and-forget instruction: a fence and an atomic would be two more memory round trips under load.
         if (done && threadIdx.x == FA_THREADS && !p.drop_arrivals) red_release_gpu_add(p.sync, done);
+        if (!SIDE_U) return;
+
+        // ---- The side warps go on to the delta term U^ h of this CTA's rows while the main warps are still streaming
+        // W_b: the wait for h, the sum of its two halves, phase U and its reduction all hide under that stream, and the
+        // main warps only add the two row buffers at the end.
+        const int sw = warp - FA_WARPS, st = threadIdx.x - FA_THREADS;
+        if (st == 0) {
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(p.sync) < static_cast<unsigned int>(n_units)) {
+                if (clock64() - t0 > p.spin_limit) {
+                    atomicExch(p.status, 1u);
+                    break;
+                }
+            }
+        }
+        side_sync();
+        __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(after_rows);    // [T][r + 8]; the staging area is free by now
+        {
+            // the two float32 halves of h, summed, rounded to bf16 once and kept in shared memory for phase U
+            const float* h0 = reinterpret_cast<const float*>(p.h);
+            const float* h1 = h0 + static_cast<size_t>(p.T) * p.r;
+            const int quads = (p.T * p.r) >> 2;
+            for (int i = st; i < quads; i += FA_SIDE_WARPS * 32) {
+                const uint4 a = ldcg16(h0 + 4 * i), b = ldcg16(h1 + 4 * i);
+                const int t = (4 * i) / p.r, k = (4 * i) % p.r;
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(__uint_as_float(a.x) + __uint_as_float(b.x),
+                                                                __uint_as_float(a.y) + __uint_as_float(b.y));
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(__uint_as_float(a.z) + __uint_as_float(b.z),
+                                                                __uint_as_float(a.w) + __uint_as_float(b.w));
+                uint2 v;
+                v.x = *reinterpret_cast<const uint32_t*>(&lo);
+                v.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(hs + static_cast<size_t>(t) * (p.r + 8) + k) = v;
+            }
+        }
+        side_sync();
+        // Re-arm the counters for the next call on this scratch buffer: every CTA checks out once it is past its wait and
+        // has read h; the last one to do so (nobody reads the counters or h of this call any more) zeroes them.
+        if (st == 0) {
+            if (atomicAdd(p.sync + 1, 1u) == static_cast<unsigned int>(G - 1)) {
+                atomicExch(p.sync, 0u);
+                atomicExch(p.sync + 1, 0u);
+                atomicExch(p.sync + 3, 0u);
+            }
+        }
+        float (*sred)[32][33] = reinterpret_cast<float (*)[32][33]>(side_red);
+        int uk = 1 << 30;                                  // no operands were prefetched for this team
+        for (int blk = row0; blk < row1; blk += FA_ROWS) {
+            float acc[2][NT][4];
+            zero_acc<NT>(acc);
+            uh_block<NT, true, FA_SIDE_WARPS>(p, acc, blk, row1, hs, nullptr, uk, sw, gid, tig);
+            float* yd = ydel + static_cast<size_t>(blk - row0) * YS;
+            reduce_tiles_team<NT, FA_SIDE_WARPS>(sred, acc, sw, gid, tig, [=](int row, int t, float v) { yd[row * YS + t] = v; });
+        }
+        asm volatile("bar.arrive 3, %0;" ::"n"(FA_THREADS + FA_SIDE_WARPS * 32) : "memory");   // the delta rows are complete
         return;
     }
     if (!SIDE) {
@@ -744,11 +818,22 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
             ybuf[static_cast<size_t>(rr) * YS + t] = __bfloat162float(p.y_dense[static_cast<size_t>(t) * p.M + row0 + rr]);
         }
     }
+    if constexpr (SIDE_U) {
+        // The side warps have computed (or are finishing) the delta term of these rows; the output is the sum of the two
+        // row buffers, one bf16 rounding.
+        asm volatile("bar.sync 3, %0;" ::"n"(FA_THREADS + FA_SIDE_WARPS * 32) : "memory");
+        const int rows = row1 - row0, T = p.T;
+        for (int e = threadIdx.x; e < rows * T; e += FA_THREADS) {
+            const int t = e / rows, rr = e - t * rows;
+            p.out[static_cast<size_t>(t) * p.M + row0 + rr] =
+                __float2bfloat16_rn(ydel[static_cast<size_t>(rr) * YS + t] + ybuf[static_cast<size_t>(rr) * YS + t]);
+        }
+        return;
+    }
     // operands of the first phase-U items: in flight while this CTA waits for h.  The stream variant reuses its
     // FIFO (drained by now), the others have an area of their own behind the h tile.
     uint8_t* ustage = FIFO ? const_cast<uint8_t*>(fifo)
-                           : reinterpret_cast<uint8_t*>(ybuf + static_cast<size_t>(p.rows_cap) * YS) +
-                                 (SIDE || p.hstage ? fa_side_region(p.T, p.r) : 0);
+                           : reinterpret_cast<uint8_t*>(after_rows) + (SIDE || p.hstage ? fa_side_region(p.T, p.r) : 0);
     if (p.upf > 0) uh_prefetch(p, ustage, row0, row1, warp, gid, tig, fa_u_split(NT));
 
     // ---- wait for every h unit (bounded; on expiry record a status and carry on)
@@ -798,7 +883,7 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
         }
         main_sync();
     }
-    __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(ybuf + static_cast<size_t>(p.rows_cap) * YS);   // [T][r + 8]
+    __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(after_rows);   // [T][r + 8]
     if (!SIDE) {
         if (p.hstage) {
             // h into shared memory in one sweep of 16-byte copies: phase U would otherwise fetch it from L2 in small
