@@ -42,7 +42,8 @@ __host__ __device__ constexpr bool fa_side(int NT) { return NT <= 2; }
 // Up to 8 tokens the side warps, once their share of h is written, also compute the delta term U^ h of their CTA's rows
 // under the main warps' stream of W_b (measured per call on B200: q_proj T = 1 11.4 -> 10.2 us, gate_proj 25.6 -> 22.7,
 // down_proj 21.1 -> 19.9).  At 9-16 tokens four warps take longer over phase U than the stream lasts (gate_proj T = 16
-// 31.0 -> 34.0 us), so there the main warps do it after their stream, as above 16 tokens.
+// 31.0 -> 34.3 us, also with their operands loaded an item ahead), so there the main warps do it after their stream, as
+// above 16 tokens.
 __host__ __device__ constexpr bool fa_side_u(int NT) { return NT == 1; }
 __host__ __device__ constexpr int fa_threads(int NT) { return FA_THREADS + (fa_side(NT) ? FA_SIDE_WARPS * 32 : 0); }
 
@@ -116,11 +117,13 @@ __host__ __device__ constexpr int fa_fifo_item(int NT) { return (8 + 2 * NT) * 1
 constexpr int FA_FIFO_MAX = 5;
 
 // without the FIFO; the launch adds stages * fa_fifo_item(NT) in front
-// With side warps (T <= 16) the side team has a reduction buffer of its own ([4][32][33]) and a second row buffer
-// (the delta term U^ h of the CTA's rows, which the side warps compute while the main warps still stream W_b).
+// With side warps (T <= 16) the side team has a reduction buffer of its own; up to 8 tokens, where it also computes the
+// delta term U^ h of the CTA's rows while the main warps still stream W_b, that buffer is [4][32][33] and there is a
+// second row buffer for the delta term.
+__host__ __device__ constexpr int fa_side_red_floats(int NT) { return fa_side(NT) ? FA_SIDE_WARPS * 32 * (fa_side_u(NT) ? 33 : 17) : 0; }
 __host__ __device__ inline size_t factored_smem_bytes(int NT, int rows_cap, int T, int r) {
-    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + (fa_side(NT) ? FA_SIDE_WARPS * 32 * 33 : 0) +
-            static_cast<size_t>(rows_cap) * (8 * NT + 1) * (fa_side(NT) ? 2 : 1)) * sizeof(float) +
+    return (static_cast<size_t>(FA_WARPS) * 32 * 33 + fa_side_red_floats(NT) +
+            static_cast<size_t>(rows_cap) * (8 * NT + 1) * (fa_side_u(NT) ? 2 : 1)) * sizeof(float) +
            (fa_side(NT) ? fa_side_region(T, r) : 0);
 }
 
@@ -598,79 +601,108 @@ __device__ __forceinline__ void uh_prefetch(const FactoredParams& p, uint8_t* us
     fa_cp_async_commit();
 }
 
+// Operands of one phase-U work item as a thread holds them: 32 codes of rows gid and gid + 8 of an m16 tile, and the
+// zero-point and scale of those rows for the item's rank group.
+struct UOperand {
+    uint4 q[2];
+    uint32_t z[2], s[2];
+};
+__device__ __forceinline__ void uh_fetch(const FactoredParams& p, UOperand& o, int blk, int row_end, int mt, int g, int gid, int tig) {
+    const int ng = p.r >> 7;
+    const size_t rowb = static_cast<size_t>(p.r >> 1);
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
+        const size_t e = static_cast<size_t>(m) * ng + g;
+        o.q[hr] = ldg16_stream(p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
+        o.z[hr] = p.uz[e];
+        o.s[hr] = p.us[e];
+    }
+}
+// acc += us * (Ucode - uz)[m16 tile mt, group g] h^T for the token tiles of `part`
+template <int NT, bool SPLIT>
+__device__ __forceinline__ void uh_compute(const FactoredParams& p, float (&acc)[2][NT][4], const UOperand& o, int mt, int g, int part,
+                                           const __nv_bfloat16* hs, int gid, int tig) {
+    constexpr int NS = fa_u_split(NT);
+    const int T = p.T, r = p.r;
+    uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
+    float su[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        const uint32_t zz = kBf2_128 | o.z[hr] | (o.z[hr] << 16);
+        su[hr] = bf16_bits_to_f32(static_cast<uint16_t>(o.s[hr]));
+        const uint32_t cw[4] = {o.q[hr].x, o.q[hr].y, o.q[hr].z, o.q[hr].w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            uint32_t ev[4];
+            unpack8_bf16(cw[wi], ev);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) a[hr][4 * wi + q4] = bf2_sub(ev[q4], zz);
+        }
+    }
+    const int kb = g * 128 + tig * 32;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        if (NS > 1 && nt / (NT / NS) != part) continue;
+        const int tok = nt * 8 + gid;
+        float pa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            uint4 hq = make_uint4(0u, 0u, 0u, 0u);
+            if (tok < T) {
+                if (SPLIT || hs != nullptr) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
+                else hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
+            }
+            mma_bf16(pa, a[0][4 * wi], a[1][4 * wi], a[0][4 * wi + 1], a[1][4 * wi + 1], hq.x, hq.y);
+            mma_bf16(pa, a[0][4 * wi + 2], a[1][4 * wi + 2], a[0][4 * wi + 3], a[1][4 * wi + 3], hq.z, hq.w);
+        }
+        // one rescale per group; mt selects the accumulator tile
+        if (mt == 0) {
+            acc[0][nt][0] += su[0] * pa[0];
+            acc[0][nt][1] += su[0] * pa[1];
+            acc[0][nt][2] += su[1] * pa[2];
+            acc[0][nt][3] += su[1] * pa[3];
+        } else {
+            acc[1][nt][0] += su[0] * pa[0];
+            acc[1][nt][1] += su[0] * pa[1];
+            acc[1][nt][2] += su[1] * pa[2];
+            acc[1][nt][3] += su[1] * pa[3];
+        }
+    }
+}
+
 // SPLIT: h has been staged in shared memory (hs, bf16 [T][r + 8]); otherwise it is read from p.h (L2).
-// k: running index of this warp's items over the blocks (the first p.upf were prefetched).
+// k: running index of this warp's items over the blocks (the first p.upf were prefetched into shared memory before the
+// grid-wide wait; the others are loaded one item ahead of their use).
 template <int NT, bool SPLIT, int TEAM = FA_WARPS>
 __device__ __forceinline__ void uh_block(const FactoredParams& p, float (&acc)[2][NT][4], int blk, int row_end,
                                          const __nv_bfloat16* hs, const uint8_t* ustage, int& k, int warp, int gid, int tig) {
-    const int T = p.T, r = p.r;
-    const int ng = r >> 7;
-    const size_t rowb = static_cast<size_t>(r >> 1);
+    const int ng = p.r >> 7;
     int g_lo, g_hi;
     fa_group_range(p, blk, min(blk + FA_ROWS, row_end), g_lo, g_hi);
     constexpr int NS = fa_u_split(NT);
-    for (int j = warp; j < 2 * (g_hi - g_lo) * NS; j += TEAM, ++k) {
+    const int n = 2 * (g_hi - g_lo) * NS;
+    UOperand cur, nxt;
+    if (warp < n && k >= p.upf) uh_fetch(p, cur, blk, row_end, (warp / NS) & 1, g_lo + ((warp / NS) >> 1), gid, tig);
+    for (int j = warp; j < n; j += TEAM, ++k) {
         const int part = j % NS, jj = j / NS;               // token tiles [part * NT / NS, (part + 1) * NT / NS)
         const int mt = jj & 1, g = g_lo + (jj >> 1);
-        uint32_t a[2][16];           // [row gid / gid+8][pair]: (code - zero) as bf16x2
-        float su[2];
+        const int jn = j + TEAM;
+        if (jn < n && k + 1 >= p.upf) uh_fetch(p, nxt, blk, row_end, (jn / NS) & 1, g_lo + ((jn / NS) >> 1), gid, tig);
+        if (k < p.upf) {
 #pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
-            const size_t e = static_cast<size_t>(m) * ng + g;
-            uint4 q;
-            uint32_t z, sbits;
-            if (k < p.upf) {
+            for (int hr = 0; hr < 2; ++hr) {
+                const int m = min(blk + mt * 16 + hr * 8 + gid, row_end - 1);
+                const size_t e = static_cast<size_t>(m) * ng + g;
                 const uint8_t* base = ustage + static_cast<size_t>(k) * FA_UPF_ITEM;
-                q = *reinterpret_cast<const uint4*>(base + (hr * FA_THREADS + threadIdx.x) * 16);
+                cur.q[hr] = *reinterpret_cast<const uint4*>(base + (hr * FA_THREADS + threadIdx.x) * 16);
                 const uint2 w = *reinterpret_cast<const uint2*>(base + 2 * FA_THREADS * 16 + (hr * FA_THREADS + threadIdx.x) * 8);
-                z = (w.x >> (8 * static_cast<uint32_t>(e & 3))) & 0xFFu;
-                sbits = (w.y >> (16 * static_cast<uint32_t>(e & 1))) & 0xFFFFu;
-            } else {
-                q = ldg16_stream(p.uq + static_cast<size_t>(m) * rowb + g * 64 + tig * 16);
-                z = p.uz[e];
-                sbits = p.us[e];
-            }
-            const uint32_t zz = kBf2_128 | z | (z << 16);
-            su[hr] = bf16_bits_to_f32(static_cast<uint16_t>(sbits));
-            const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                uint32_t ev[4];
-                unpack8_bf16(cw[wi], ev);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) a[hr][4 * wi + q4] = bf2_sub(ev[q4], zz);
+                cur.z[hr] = (w.x >> (8 * static_cast<uint32_t>(e & 3))) & 0xFFu;
+                cur.s[hr] = (w.y >> (16 * static_cast<uint32_t>(e & 1))) & 0xFFFFu;
             }
         }
-        const int kb = g * 128 + tig * 32;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            if (NS > 1 && nt / (NT / NS) != part) continue;
-            const int tok = nt * 8 + gid;
-            float pa[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                uint4 hq = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < T) {
-                    if (SPLIT || hs != nullptr) hq = *reinterpret_cast<const uint4*>(hs + static_cast<size_t>(tok) * (r + 8) + kb + 8 * wi);
-                    else hq = ldcg16(p.h + static_cast<size_t>(tok) * r + kb + 8 * wi);
-                }
-                mma_bf16(pa, a[0][4 * wi], a[1][4 * wi], a[0][4 * wi + 1], a[1][4 * wi + 1], hq.x, hq.y);
-                mma_bf16(pa, a[0][4 * wi + 2], a[1][4 * wi + 2], a[0][4 * wi + 3], a[1][4 * wi + 3], hq.z, hq.w);
-            }
-            // one rescale per group; mt selects the accumulator tile
-            if (mt == 0) {
-                acc[0][nt][0] += su[0] * pa[0];
-                acc[0][nt][1] += su[0] * pa[1];
-                acc[0][nt][2] += su[1] * pa[2];
-                acc[0][nt][3] += su[1] * pa[3];
-            } else {
-                acc[1][nt][0] += su[0] * pa[0];
-                acc[1][nt][1] += su[0] * pa[1];
-                acc[1][nt][2] += su[1] * pa[2];
-                acc[1][nt][3] += su[1] * pa[3];
-            }
-        }
+        uh_compute<NT, SPLIT>(p, acc, cur, mt, g, part, hs, gid, tig);
+        cur = nxt;
     }
 }
 
@@ -696,10 +728,10 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
     constexpr int YS = 8 * NT + 1;                         // padded row stride of the y buffer
     constexpr bool SIDE = fa_side(NT);
     constexpr bool SIDE_U = fa_side_u(NT);                 // the side warps also compute the delta term (phase U)
-    float* side_red = fsmem + FA_WARPS * 32 * 33;          // [4][32][33], the side team's reduction buffer
-    float* ybuf = side_red + (SIDE ? FA_SIDE_WARPS * 32 * 33 : 0);     // [rows_cap][YS] base term of the CTA's rows
-    float* ydel = ybuf + static_cast<size_t>(p.rows_cap) * YS;         // [rows_cap][YS] delta term (side warps only)
-    float* after_rows = ybuf + static_cast<size_t>(p.rows_cap) * YS * (SIDE ? 2 : 1);
+    float* side_red = fsmem + FA_WARPS * 32 * 33;          // the side team's reduction buffer
+    float* ybuf = side_red + fa_side_red_floats(NT);       // [rows_cap][YS] base term of the CTA's rows
+    float* ydel = ybuf + static_cast<size_t>(p.rows_cap) * YS;         // [rows_cap][YS] delta term (SIDE_U only)
+    float* after_rows = ybuf + static_cast<size_t>(p.rows_cap) * YS * (SIDE_U ? 2 : 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int G = gridDim.x, c = blockIdx.x;
     const int parts = SIDE ? 2 : p.parts;                  // slices of d_i per 16 ranks (side warps: two halves)
@@ -770,11 +802,42 @@ __global__ void __launch_bounds__(fa_threads(NT)) factored_kernel(const Factored
             }
         }
         float (*sred)[32][33] = reinterpret_cast<float (*)[32][33]>(side_red);
-        int uk = 1 << 30;                                  // no operands were prefetched for this team
+        // Phase U over the CTA's row blocks.  A warp's items are (m16 tile, rank group) pairs, item j of a block going
+        // to warp j % 4; the operands of the next item, which may belong to the next block, are requested before the
+        // current one is multiplied, so that their latency also hides under the reduction at the end of a block.
+        auto items_of = [&](int blk, int& g_lo) {
+            int g_hi;
+            fa_group_range(p, blk, min(blk + FA_ROWS, row1), g_lo, g_hi);
+            return 2 * (g_hi - g_lo);
+        };
+        UOperand cur, nxt;
+        int nb = row0, nj = sw, n_glo = 0, n_n = 0;          // the next item to fetch: block, index, its block's first group and item count
+        auto advance = [&]() {                                // moves (nb, nj) to the warp's next existing item, fetching it
+            while (nb < row1) {
+                n_n = items_of(nb, n_glo);
+                if (nj < n_n) {
+                    uh_fetch(p, nxt, nb, row1, nj & 1, n_glo + (nj >> 1), gid, tig);
+                    return;
+                }
+                nb += FA_ROWS;
+                nj = sw;
+            }
+        };
+        advance();
         for (int blk = row0; blk < row1; blk += FA_ROWS) {
             float acc[2][NT][4];
             zero_acc<NT>(acc);
-            uh_block<NT, true, FA_SIDE_WARPS>(p, acc, blk, row1, hs, nullptr, uk, sw, gid, tig);
+            while (nb == blk) {                               // every fetched item of this block
+                cur = nxt;
+                const int mt = nj & 1, g = n_glo + (nj >> 1);
+                nj += FA_SIDE_WARPS;
+                if (nj >= n_n) {
+                    nb += FA_ROWS;
+                    nj = sw;
+                }
+                advance();
+                uh_compute<NT, true>(p, acc, cur, mt, g, 0, hs, gid, tig);
+            }
             float* yd = ydel + static_cast<size_t>(blk - row0) * YS;
             reduce_tiles_team<NT, FA_SIDE_WARPS>(sred, acc, sw, gid, tig, [=](int row, int t, float v) { yd[row * YS + t] = v; });
         }
