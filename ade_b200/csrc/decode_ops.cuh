@@ -34,14 +34,16 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
     const bool vec = (H & 7) == 0 && H <= 8192 &&
                      ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(rr)) & 15) == 0;
     const int nvec = H >> 3;
-    uint4 xv[4];
+    uint4 xv[4], wv4[4];
     float s = 0.f;
     if (vec) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int i = threadIdx.x + k * 256;
             xv[k] = make_uint4(0u, 0u, 0u, 0u);
+            wv4[k] = make_uint4(0u, 0u, 0u, 0u);
             if (i < nvec) {
+                wv4[k] = reinterpret_cast<const uint4*>(w)[i];       // requested together with the row: one memory round trip
                 xv[k] = reinterpret_cast<const uint4*>(xr)[i];
                 if (rr) {
                     const uint4 rv = reinterpret_cast<const uint4*>(rr)[i];
@@ -91,9 +93,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
         for (int k = 0; k < 4; ++k) {
             const int i = threadIdx.x + k * 256;
             if (i < nvec) {
-                const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
                 const uint32_t xx[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                const uint32_t ww[4] = {wv4[k].x, wv4[k].y, wv4[k].z, wv4[k].w};
                 uint32_t oo[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {

@@ -347,7 +347,10 @@ class GreedyGraphDecoder:
             torch.cuda.current_stream().wait_stream(side)
             del spare
             cache = StaticCache(config=cfg, max_cache_len=max_len)
-            self._step(cache, tok, pos)                        # allocates the cache's tensors outside the capture
+            # two steps outside the capture: the first allocates the cache's tensors (lazily, inside transformers), the
+            # second lets code that only engages on an initialised cache (the fused attention step) allocate its own
+            for _ in range(2):
+                self._step(cache, tok, pos)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 nxt = self._step(cache, tok, pos)

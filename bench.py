@@ -644,6 +644,7 @@ def run_case(argv):
 
         python bench.py --case recon [M N r]          default 11008 4096 512 (Llama-2-7B gate_proj delta)
         python bench.py --case factored [T M N r]     default 16 4096 4096 256 (q_proj delta)
+        python bench.py --case decode                 one graph replay of the 7B-architecture decode step (launch list)
     """
     import torch
 
@@ -669,6 +670,22 @@ def run_case(argv):
             kernels.factored_forward(x, p4, weight=W)
         torch.cuda.synchronize()
         print(f"factored T={T} {M}x{N} r={r}: 4 launches, status {kernels.factored_status(dev, T, r)}")
+    elif what == "decode":
+        # one replay of the captured decode step of the 7B-architecture model between cudaProfilerStart / Stop
+        from ade_b200.serving import GreedyGraphDecoder
+
+        model, ranks, groups = synth.synthetic_llama("7b", seed=0, device=dev)
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 32000, (1, 64), generator=g).to(dev)
+        dec = GreedyGraphDecoder(model)
+        dec.generate(ids, 8)
+        torch.cuda.synchronize()
+        graph = dec._captured(1, 64 + 8 + 1, torch.device(dev))[0]
+        torch.cuda.profiler.start()
+        graph.replay()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(f"decode step of a 7B-architecture model replayed once: {len(ranks)} delta modules, {groups} fused groups")
     else:
         raise SystemExit(run_case.__doc__)
 
