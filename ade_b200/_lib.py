@@ -43,7 +43,8 @@ EXPORTS = (
     "ade_b200_device_status", "ade_b200_version", "ade_b200_last_cuda_error",
     "ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_compress_rows",
     "ade_b200_factored_scratch_bytes", "ade_b200_factored_sync_offset", "ade_b200_factored",
-    "ade_b200_factored_static", "ade_b200_factored_static_status", "ade_b200_recon", "ade_b200_set_option",
+    "ade_b200_factored_static", "ade_b200_factored_static_status", "ade_b200_recon", "ade_b200_expand_codes",
+    "ade_b200_recon_expanded", "ade_b200_set_option",
     "ade_b200_rmsnorm", "ade_b200_add_rmsnorm", "ade_b200_rope", "ade_b200_silu_mul", "ade_b200_attn_decode",
 )
 
@@ -94,6 +95,8 @@ def load() -> ctypes.CDLL:
     lib.ade_b200_factored_static.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, ci, vp]
     lib.ade_b200_factored_static.restype = ci
     lib.ade_b200_recon.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp]
+    lib.ade_b200_expand_codes.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp]
+    lib.ade_b200_recon_expanded.argtypes = [ctypes.POINTER(AdeDelta), vp, vp, vp, vp, vp, vp, vp]
     lib.ade_b200_factored_static_status.argtypes = [vp, ci, vp]
     lib.ade_b200_factored_static_status.restype = ci
     ll = ctypes.c_longlong
@@ -106,7 +109,8 @@ def load() -> ctypes.CDLL:
         getattr(lib, name).restype = ci
     lib.ade_b200_set_option.argtypes = [ci, ctypes.c_longlong]
     lib.ade_b200_set_option.restype = ci
-    for name in ("ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_factored", "ade_b200_recon"):
+    for name in ("ade_b200_pack_codes", "ade_b200_pack_zeros", "ade_b200_factored", "ade_b200_recon", "ade_b200_expand_codes",
+                 "ade_b200_recon_expanded"):
         getattr(lib, name).restype = ci
     _lib = lib
     return lib

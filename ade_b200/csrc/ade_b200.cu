@@ -68,7 +68,11 @@ int device_info(const DeviceInfo** out) {
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
-                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
                 return ADE_ERR_CUDA;
             if (!cuda_ok(cudaFuncSetAttribute(ade::compress_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               static_cast<int>(ade::compress_smem_bytes(ade::CQ_MAX_RANK, true)))))
@@ -566,8 +570,40 @@ int ade_b200_set_option(int option, long long value) {
     }
 }
 
+int ade_b200_expand_codes(const ade_delta_t* d, void* u8, void* v8, void* stream) {
+    int rc = check_delta(d);
+    if (rc) return rc;
+    if (!d->vq || !u8 || !v8) return ADE_ERR_NULL;
+    if (!aligned16(d->vq) || !aligned16(u8) || !aligned16(v8)) return ADE_ERR_ALIGN;
+    const DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc) return rc;
+    const int ng = d->r / ADE_B200_GROUP;
+    const long long chunks = (static_cast<long long>(d->M) + d->N) * ng * 4;
+    const long long want = (chunks + 255) / 256;
+    const int grid = static_cast<int>(want < 8ll * di->sms ? want : 8ll * di->sms);
+    ade::expand_codes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(d->uq, d->uz, d->vq, d->vz, static_cast<uint8_t*>(u8),
+                                                                                 static_cast<uint8_t*>(v8), d->M, d->N, ng);
+    return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+}
+
+static int recon_impl(const ade_delta_t* d, const void* u8, const void* v8, const void* w_b, void* w_out, int32_t* dbg_acc,
+                      int* status_dev, void* stream);
+
 int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* dbg_acc, int* status_dev,
                    void* stream) {
+    return recon_impl(d, nullptr, nullptr, w_b, w_out, dbg_acc, status_dev, stream);
+}
+
+int ade_b200_recon_expanded(const ade_delta_t* d, const void* u8, const void* v8, const void* w_b, void* w_out,
+                            int32_t* dbg_acc, int* status_dev, void* stream) {
+    if (!u8 || !v8) return ADE_ERR_NULL;
+    if (!aligned16(u8) || !aligned16(v8)) return ADE_ERR_ALIGN;
+    return recon_impl(d, u8, v8, w_b, w_out, dbg_acc, status_dev, stream);
+}
+
+static int recon_impl(const ade_delta_t* d, const void* u8, const void* v8, const void* w_b, void* w_out, int32_t* dbg_acc,
+                      int* status_dev, void* stream) {
     int rc = check_delta(d);
     if (rc) return rc;
     if (!d->vq || !w_b || !w_out) return ADE_ERR_NULL;
@@ -601,7 +637,7 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
     const int ng = d->r / ADE_B200_GROUP;
     const int ntiles = ((d->M + ade::RC_TILE - 1) / ade::RC_TILE) * (d->N / ade::RC_TILE);
     const int grid = ntiles < di->sms ? ntiles : di->sms;
-    if (ng <= ade::RS_MAX_GROUPS && ade::recon_strip_smem_bytes(ng) <= static_cast<size_t>(kMaxSmem)) {
+    if (ng <= ade::RS_MAX_GROUPS && ade::recon_strip_smem_bytes(ng, u8 != nullptr) <= static_cast<size_t>(kMaxSmem)) {
         // ranks up to 1024: the strip-resident kernel, all global traffic through tensor maps
         if (!load_encode_tiled()) return ADE_ERR_CUDA;
         ade::ReconMaps maps;
@@ -611,8 +647,22 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out, int32_t* 
             !make_map_2d(&maps.uq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->uq, rb, M, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE) ||
             !make_map_2d(&maps.vq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->vq, rb, N, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE))
             return ADE_ERR_CUDA;
-        const size_t smem = ade::recon_strip_smem_bytes(ng);
+        const size_t smem = ade::recon_strip_smem_bytes(ng, u8 != nullptr);
         const cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (u8) {
+            const uint64_t r = static_cast<uint64_t>(d->r);
+            if (!make_map_2d(&maps.u8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, u8, r, M, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+                !make_map_2d(&maps.v8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, v8, r, N, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+                return ADE_ERR_CUDA;
+            if (ng > 4) {
+                if (dbg_acc) ade::recon_strip_kernel<true, true, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
+                else ade::recon_strip_kernel<false, true, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
+            } else {
+                if (dbg_acc) ade::recon_strip_kernel<true, false, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
+                else ade::recon_strip_kernel<false, false, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
+            }
+            return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;
+        }
         if (ng > 4) {
             if (dbg_acc) ade::recon_strip_kernel<true, true><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);
             else ade::recon_strip_kernel<false, true><<<grid, ade::RS_THREADS, smem, st>>>(p, maps);

@@ -19,6 +19,12 @@
 //   warp  21    one thread issues the TMA copies of packed codes and V zero-points (raw ring).
 //   warp  22    scales: bf16 us / vs of the next tile -> float32 tables in shared memory (two buffers).
 // Every mbarrier wait is bounded as in recon.cuh (abort flag, status word, normal exit).
+//
+// Expanded operands (template parameter EXP): when the caller has run expand_codes_kernel once (int8 code minus
+// zero-point, (M + N) * r bytes), the load thread copies the operand tiles by TMA with the 128-byte swizzle straight
+// into the resident strip and the V stages; the unpack role and the raw ring do not exist (19 warps, five V stages).
+// The unpack warps were one of three roles that each needed about as long per group as the epilogue, and they
+// took issue slots from it: gate_proj (11008 x 4096, r = 512) 75 -> 63 us per launch, same bits.
 #pragma once
 #include <cuda.h>
 
@@ -32,6 +38,9 @@ constexpr int RS_MMA_WARP = 20;
 constexpr int RS_LOAD_WARP = 21;
 constexpr int RS_SCALE_WARP = 22;
 constexpr int RS_THREADS = 23 * 32;
+// Expanded operands (int8 codes minus zero-point, prepared once by expand_codes_kernel): no unpack role, the operand
+// tiles arrive by TMA in their 128-byte-swizzled form; the three single roles move down to warps 16-18.
+constexpr int RS_THREADS_EXP = 19 * 32;
 constexpr int RS_OPER_BYTES = RC_TILE * 128;             // one int8 operand tile of one group
 constexpr int RS_RAW_CODES = RC_TILE * 64;               // 128 rows x 64 bytes of nibbles
 constexpr int RS_RAW_SLOT = RS_RAW_CODES + 256;          // + 128 zero-points, padded
@@ -46,16 +55,18 @@ struct ReconMaps {
     CUtensorMap out;    // same geometry
     CUtensorMap uq;     // (M, r/2) bytes, box 128 rows x 64 bytes
     CUtensorMap vq;     // (N, r/2) bytes, box 128 rows x 64 bytes
+    CUtensorMap u8;     // expanded operands only: (M, r) int8, box 128 rows x 128 bytes, 128-byte swizzle
+    CUtensorMap v8;     // (N, r) int8, same box
 };
 
 // Ring depths and barrier indices.  BIG (five to eight groups): the resident strip takes up to 128 KB, so the
 // rings shrink to two V stages, two raw slots and one box buffer per warp (measured: ring depth is not what
 // limits this kernel).
-template <bool BIG>
+template <bool BIG, bool EXP = false>
 struct RsCfg {
     static constexpr int GROUPS = BIG ? 8 : 4;           // resident groups at most
-    static constexpr int B_STAGES = BIG ? 2 : 3;         // int8 V tiles in flight
-    static constexpr int RAW_DEPTH = BIG ? 2 : 4;        // packed items in flight
+    static constexpr int B_STAGES = EXP ? (BIG ? 3 : 5) : (BIG ? 2 : 3);   // int8 V tiles in flight
+    static constexpr int RAW_DEPTH = EXP ? 0 : (BIG ? 2 : 4);                // packed items in flight
     static constexpr int WB_BUFS = BIG ? 1 : 2;          // box buffers per epilogue warp
     static constexpr int WB_BYTES = RS_EPI_WARPS * WB_BUFS * RS_BOX_BYTES;
     // barrier indices (8 bytes each)
@@ -77,7 +88,8 @@ struct RsCfg {
     }
 };
 
-__host__ __device__ inline size_t recon_strip_smem_bytes(int ng) {
+__host__ __device__ inline size_t recon_strip_smem_bytes(int ng, bool expanded = false) {
+    if (expanded) return ng > 4 ? RsCfg<true, true>::smem_bytes(ng) : RsCfg<false, true>::smem_bytes(ng);
     return ng > 4 ? RsCfg<true>::smem_bytes(ng) : RsCfg<false>::smem_bytes(ng);
 }
 
@@ -99,9 +111,45 @@ __device__ __forceinline__ void unpack_store_s(uint32_t tile, int row, int c, ui
     sts16(rp + (((2 * c + 1) ^ sw) << 4), make_uint4(o[4], o[5], o[6], o[7]));
 }
 
-template <bool DBG, bool BIG>
-__global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconParams p, const __grid_constant__ ReconMaps maps) {
-    using C = RsCfg<BIG>;
+// Packed codes -> int8 operands (code minus zero-point) in the byte order the unpack role of recon_strip_kernel
+// produces: thread t turns the t-th 16-byte chunk of a (rows, r/2) code array into the t-th 32-byte chunk of the
+// (rows, r) int8 array.  U zero-points are (M, ng) bytes, V zero-points (ng, N).
+__global__ void __launch_bounds__(256) expand_codes_kernel(const uint8_t* __restrict__ uq, const uint8_t* __restrict__ uz,
+                                                           const uint8_t* __restrict__ vq, const uint8_t* __restrict__ vz,
+                                                           uint8_t* __restrict__ u8, uint8_t* __restrict__ v8, int M, int N, int ng) {
+    const long long nu = static_cast<long long>(M) * ng * 4, total = nu + static_cast<long long>(N) * ng * 4;
+    for (long long t = blockIdx.x * 256ll + threadIdx.x; t < total; t += gridDim.x * 256ll) {
+        const bool is_u = t < nu;
+        const long long e = is_u ? t : t - nu;
+        const long long rg = e >> 2;                       // row * ng + group
+        uint32_t z;
+        if (is_u) {
+            z = uz[rg];
+        } else {
+            const long long row = rg / ng;
+            z = vz[(rg - row * ng) * N + row];
+        }
+        const uint4 q = *reinterpret_cast<const uint4*>((is_u ? uq : vq) + e * 16);
+        const uint32_t zk = 0x80808080u - z * 0x01010101u;
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = ((w[i] & 0x0F0F0F0Fu) + zk) ^ 0x80808080u;
+            o[2 * i + 1] = (((w[i] >> 4) & 0x0F0F0F0Fu) + zk) ^ 0x80808080u;
+        }
+        uint4* dst = reinterpret_cast<uint4*>((is_u ? u8 : v8) + e * 32);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+template <bool DBG, bool BIG, bool EXP = false>
+__global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_strip_kernel(const ReconParams p, const __grid_constant__ ReconMaps maps) {
+    using C = RsCfg<BIG, EXP>;
+    constexpr int MMA_WARP = EXP ? RS_EPI_WARPS : RS_MMA_WARP;
+    constexpr int LOAD_WARP = MMA_WARP + 1;
+    constexpr int SCALE_WARP = MMA_WARP + 2;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
     const uint32_t base = (raw0 + 1023u) & ~1023u;
@@ -124,10 +172,10 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             mbar_init(bar(C::BAR_RAW_EMPTY + i), 4);
         }
         for (int i = 0; i < C::B_STAGES; ++i) {
-            mbar_init(bar(C::BAR_B_FULL + i), 4);
+            mbar_init(bar(C::BAR_B_FULL + i), EXP ? 1 : 4);
             mbar_init(bar(C::BAR_B_EMPTY + i), 1);
         }
-        for (int i = 0; i < C::GROUPS; ++i) mbar_init(bar(C::BAR_A_FULL + i), 4);
+        for (int i = 0; i < C::GROUPS; ++i) mbar_init(bar(C::BAR_A_FULL + i), EXP ? 1 : 4);
         mbar_init(bar(C::BAR_A_FREE), 1);
         for (int i = 0; i < RS_ACC_STAGES; ++i) {
             mbar_init(bar(C::BAR_TFULL + i), 1);
@@ -141,7 +189,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == RS_MMA_WARP) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(tmem_slot), RS_TMEM_COLS);
         tmem_relinquish();
     }
@@ -312,7 +360,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
         }
         if (lane == 0) bulk_wait_group_read<0>();    // shared memory may go once the last store has read it
-    } else if (warp < RS_MMA_WARP) {
+    } else if (!EXP && warp < MMA_WARP) {
         // ------------------------------------------------------------------ unpack
         const int pt = threadIdx.x - RS_EPI_WARPS * 32;
         const int c = pt & 3, rbase = pt >> 2;
@@ -389,10 +437,11 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
         }
     } else {
-    if (warp == RS_MMA_WARP) {
+    if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
+        // (two issuing threads taking alternate groups were tried with the expanded operands: no faster)
         if (lane == 0) {
-            uint32_t it = 0, bi = 0, k = 0;
+            uint32_t it = 0, k = 0, s = 0, bph = 0;
 #ifdef ADE_TRACE
             int tcn = 0;
 #endif
@@ -401,9 +450,8 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                 const bool first = tile == t_begin || nt == 0;
                 const bool last = tile == t_end - 1 || nt + 1 == tiles_n;
                 if (++nt == tiles_n) nt = 0;
-                for (int g = 0; g < ng; ++g, ++it, ++bi) {
+                for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                    const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
                     ADE_TRACE_STAMP(p, tcn, 3, 0x2000 | g);
                     wait_bounded(bar(C::BAR_TEMPTY + a), aph, wctx, 4);
                     ADE_TRACE_STAMP(p, tcn, 3, 0x2100 | g);
@@ -420,12 +468,48 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
                     tc_commit(bar(C::BAR_TFULL + a));
                     if (last && g == ng - 1) tc_commit(bar(C::BAR_A_FREE));    // the strip of U may be overwritten
                     ADE_TRACE_STAMP(p, tcn, 3, 0x2300 | g);
+                    if (++s == C::B_STAGES) {
+                        s = 0;
+                        bph ^= 1;
+                    }
                 }
                 if (last) ++k;
             }
         }
         __syncwarp();
-    } else if (warp == RS_LOAD_WARP) {
+    } else if (EXP && warp == LOAD_WARP) {
+        // ------------------------------------------------------------------ expanded operands -> strip and V stages
+        if (lane == 0 && !p.drop_loads) {
+            prefetch_tensormap(&maps.u8);
+            prefetch_tensormap(&maps.v8);
+            uint32_t bi = 0, sk = 0;
+            int cur_strip = -1;
+            int sm = strip0, nt = nt0;
+            for (int tile = t_begin; tile < t_end; ++tile) {
+                const int strip = sm, n0 = nt << 7;
+                if (++nt == tiles_n) {
+                    nt = 0;
+                    ++sm;
+                }
+                if (strip != cur_strip) {
+                    cur_strip = strip;
+                    if (sk > 0) wait_bounded(bar(C::BAR_A_FREE), (sk - 1) & 1, wctx, 7);   // old strip's MMAs retired
+                    for (int g = 0; g < ng; ++g) {
+                        mbar_arrive_expect_tx(bar(C::BAR_A_FULL + g), RS_OPER_BYTES);
+                        tma_load_2d(a_res + g * RS_OPER_BYTES, &maps.u8, g * 128, strip << 7, bar(C::BAR_A_FULL + g));
+                    }
+                    ++sk;
+                }
+                for (int g = 0; g < ng; ++g, ++bi) {
+                    const uint32_t s = bi % C::B_STAGES, bph = (bi / C::B_STAGES) & 1;
+                    wait_bounded(bar(C::BAR_B_EMPTY + s), bph ^ 1, wctx, 2);
+                    mbar_arrive_expect_tx(bar(C::BAR_B_FULL + s), RS_OPER_BYTES);
+                    tma_load_2d(b_st + s * RS_OPER_BYTES, &maps.v8, g * 128, n0, bar(C::BAR_B_FULL + s));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == LOAD_WARP) {
         // ------------------------------------------------------------------ packed codes -> raw ring
         if (lane == 0 && !p.drop_loads) {                   // diagnostic drop_loads: nothing arrives, the waits run out
             prefetch_tensormap(&maps.uq);
@@ -463,7 +547,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
             }
         }
         __syncwarp();
-    } else if (warp == RS_SCALE_WARP) {
+    } else if (warp == SCALE_WARP) {
         // ------------------------------------------------------------------ scale tables, one tile ahead
         int j = 0, sm = strip0, nt = nt0;
         for (int tile = t_begin; tile < t_end; ++tile, ++j) {
@@ -524,7 +608,7 @@ __global__ void __launch_bounds__(RS_THREADS, 1) recon_strip_kernel(const ReconP
     drain_after_abort(abort_flag);
     tc_fence_before();
     __syncthreads();
-    if (warp == RS_MMA_WARP) tmem_dealloc(tmem_base, RS_TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, RS_TMEM_COLS);
 }
 
 }  // namespace ade

@@ -4,7 +4,8 @@
 // but contains no kernel: everything it does is fill an ade_delta_t and call libade_b200.so.
 //
 //   torch.ops.ade_b200.factored(x, weight?, y_dense?, uq, vq, vt, us, uz, vs, vz, M, N, r, blocks, scratch) -> out
-//   torch.ops.ade_b200.recon(base, uq, vq, vt, us, uz, vs, vz, M, N, r, dbg_acc?, status?) -> merged
+//   torch.ops.ade_b200.recon(base, uq, vq, vt, us, uz, vs, vz, M, N, r, dbg_acc?, status?, u8?, v8?) -> merged
+//   torch.ops.ade_b200.expand(uq, vq, vt, us, uz, vs, vz, M, N, r) -> (u8, v8)
 //
 // Built with the host compiler only (no nvcc): `python -m ade_b200.build`.
 #include <ATen/ATen.h>
@@ -98,7 +99,14 @@ at::Tensor factored(const at::Tensor& x, const c10::optional<at::Tensor>& weight
 
 at::Tensor recon(const at::Tensor& base, const at::Tensor& uq, const at::Tensor& vq, const at::Tensor& vt, const at::Tensor& us,
                  const at::Tensor& uz, const at::Tensor& vs, const at::Tensor& vz, int64_t M, int64_t N, int64_t r,
-                 const c10::optional<at::Tensor>& dbg_acc, const c10::optional<at::Tensor>& status) {
+                 const c10::optional<at::Tensor>& dbg_acc, const c10::optional<at::Tensor>& status,
+                 const c10::optional<at::Tensor>& u8, const c10::optional<at::Tensor>& v8) {
+    TORCH_CHECK(u8.has_value() == v8.has_value(), "u8 and v8 come together");
+    if (u8.has_value())
+        TORCH_CHECK(u8->scalar_type() == at::kChar && v8->scalar_type() == at::kChar && u8->is_contiguous() && v8->is_contiguous() &&
+                        u8->dim() == 2 && v8->dim() == 2 && u8->size(0) == M && u8->size(1) == r && v8->size(0) == N && v8->size(1) == r &&
+                        u8->device() == base.device() && v8->device() == base.device(),
+                    "expanded operands must be contiguous int8 (d_o, r) and (d_i, r) tensors on the device of base");
     TORCH_CHECK(base.is_cuda() && base.scalar_type() == at::kBFloat16 && base.dim() == 2 && base.size(0) == M && base.size(1) == N,
                 "base must be a CUDA bfloat16 (", M, ", ", N, ") tensor");
     const at::Tensor b = base.contiguous();
@@ -112,12 +120,28 @@ at::Tensor recon(const at::Tensor& base, const at::Tensor& uq, const at::Tensor&
     const c10::cuda::CUDAGuard guard(base.device());
     const ade_delta_t d = make_delta(uq, vq, vt, us, uz, vs, vz, M, N, r, {}, base);
     at::Tensor out = at::empty_like(b);
-    const int rc = ade_b200_recon(&d, b.data_ptr(), out.data_ptr(), dbg_acc.has_value() ? static_cast<int32_t*>(dbg_acc->data_ptr()) : nullptr,
-                                  status.has_value() ? static_cast<int*>(status->data_ptr()) : nullptr,
-                                  c10::cuda::getCurrentCUDAStream(base.get_device()).stream());
+    int32_t* dbg = dbg_acc.has_value() ? static_cast<int32_t*>(dbg_acc->data_ptr()) : nullptr;
+    int* st = status.has_value() ? static_cast<int*>(status->data_ptr()) : nullptr;
+    void* stream = c10::cuda::getCurrentCUDAStream(base.get_device()).stream();
+    const int rc = u8.has_value() ? ade_b200_recon_expanded(&d, u8->data_ptr(), v8->data_ptr(), b.data_ptr(), out.data_ptr(), dbg, st, stream)
+                                  : ade_b200_recon(&d, b.data_ptr(), out.data_ptr(), dbg, st, stream);
     TORCH_CHECK(rc == ADE_OK, "ade_b200_recon: ", err_name(rc), rc == ADE_ERR_CUDA ? " (cudaError " : "",
                 rc == ADE_ERR_CUDA ? std::to_string(ade_b200_last_cuda_error()) + ")" : std::string());
     return out;
+}
+
+// int8 operands (code minus zero-point) of a stored form, for recon(..., u8, v8)
+std::tuple<at::Tensor, at::Tensor> expand(const at::Tensor& uq, const at::Tensor& vq, const at::Tensor& vt, const at::Tensor& us,
+                                          const at::Tensor& uz, const at::Tensor& vs, const at::Tensor& vz, int64_t M, int64_t N, int64_t r) {
+    TORCH_CHECK(uq.is_cuda(), "stored form must be on a CUDA device");
+    const c10::cuda::CUDAGuard guard(uq.device());
+    const ade_delta_t d = make_delta(uq, vq, vt, us, uz, vs, vz, M, N, r, {}, uq);
+    at::Tensor u8 = at::empty({M, r}, uq.options().dtype(at::kChar));
+    at::Tensor v8 = at::empty({N, r}, uq.options().dtype(at::kChar));
+    const int rc = ade_b200_expand_codes(&d, u8.data_ptr(), v8.data_ptr(), c10::cuda::getCurrentCUDAStream(uq.get_device()).stream());
+    TORCH_CHECK(rc == ADE_OK, "ade_b200_expand_codes: ", err_name(rc), rc == ADE_ERR_CUDA ? " (cudaError " : "",
+                rc == ADE_ERR_CUDA ? std::to_string(ade_b200_last_cuda_error()) + ")" : std::string());
+    return {u8, v8};
 }
 
 }  // namespace
@@ -126,10 +150,12 @@ TORCH_LIBRARY(ade_b200, m) {
     m.def("factored(Tensor x, Tensor? weight, Tensor? y_dense, Tensor uq, Tensor vq, Tensor vt, Tensor us, Tensor uz, Tensor vs, Tensor vz, "
           "int M, int N, int r, int[] blocks, Tensor scratch) -> Tensor");
     m.def("recon(Tensor base, Tensor uq, Tensor vq, Tensor vt, Tensor us, Tensor uz, Tensor vs, Tensor vz, int M, int N, int r, "
-          "Tensor? dbg_acc, Tensor? status) -> Tensor");
+          "Tensor? dbg_acc, Tensor? status, Tensor? u8, Tensor? v8) -> Tensor");
+    m.def("expand(Tensor uq, Tensor vq, Tensor vt, Tensor us, Tensor uz, Tensor vs, Tensor vz, int M, int N, int r) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(ade_b200, CUDA, m) {
     m.impl("factored", &factored);
     m.impl("recon", &recon);
+    m.impl("expand", &expand);
 }

@@ -307,11 +307,27 @@ def decode_forward_packed(x, y_dense, p4, group_size=GROUP, split_k=False):
     return factored_forward(x, p4, y_dense=y_dense)
 
 
-def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None):
+def expand_codes(p4):
+    """(u8, v8): the int8 operands of the reconstruction, code minus zero-point, (d_o, r) and (d_i, r).
+
+    The reference's kernel unpacks nibbles and subtracts zero-points in its main loop on every call
+    (src/kernels.py:296-331).  A module that reconstructs often does it once: `recon_int4(..., expanded=(u8, v8))`
+    reads these arrays by TMA straight into the operand tiles and has no unpack role.  Costs (d_o + d_i) * r bytes
+    (twice the packed codes)."""
+    M, N, r = int(p4["M"]), int(p4["N"]), int(p4["r"])
+    with _on_device(p4["uq"].device):
+        try:
+            return _lib.ops().expand(p4["uq"], p4["vq"], p4["vt"], p4["us"], p4["uz"], p4["vs"], p4["vz"], M, N, r)
+        except RuntimeError as e:
+            raise _kernel_error(e) from None
+
+
+def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None, expanded=None):
     """W_b + U^ V^^T of one module in bfloat16 (same role as src/kernels.py:431-444).
 
     `dbg_acc`: optional int32 (ng, d_o, d_i) CUDA tensor that receives every group's INT32
-    accumulator; `status`: optional int32 CUDA scalar tensor for the kernel's timeout code.
+    accumulator; `status`: optional int32 CUDA scalar tensor for the kernel's timeout code;
+    `expanded`: optional (u8, v8) from `expand_codes(p4)`: same result, bit for bit, from the faster kernel.
     """
     if group_size != GROUP:
         raise ValueError("the kernels are specialised for group size 128")
@@ -323,6 +339,8 @@ def recon_int4(p4, base, group_size=GROUP, dbg_acc=None, status=None):
         raise ValueError("dbg_acc must be a contiguous int32 (ng, d_o, d_i) tensor")
     with _on_device(base.device):
         try:
-            return _lib.ops().recon(base, p4["uq"], p4["vq"], p4["vt"], p4["us"], p4["uz"], p4["vs"], p4["vz"], M, N, r, dbg_acc, status)
+            u8, v8 = expanded if expanded is not None else (None, None)
+            return _lib.ops().recon(base, p4["uq"], p4["vq"], p4["vt"], p4["us"], p4["uz"], p4["vs"], p4["vz"], M, N, r, dbg_acc, status,
+                                    u8, v8)
         except RuntimeError as e:
             raise _kernel_error(e) from None

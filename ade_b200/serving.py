@@ -13,8 +13,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .kernels import (GROUP, STORED_KEYS, decode_forward_packed, decode_kernel_status, factored_forward, pack_int4,
-                      recon_int4, recon_kernel_status)
+from .kernels import (GROUP, STORED_KEYS, decode_forward_packed, decode_kernel_status, expand_codes, factored_forward,
+                      pack_int4, recon_int4, recon_kernel_status)
 
 # Up to this many tokens the base GEMM x W_b^T runs inside the factored kernel (one launch, W_b streamed once by
 # a kernel built for skinny operands, h computed by side warps under the stream).  Above it cuBLAS is faster at the
@@ -22,6 +22,8 @@ from .kernels import (GROUP, STORED_KEYS, decode_forward_packed, decode_kernel_s
 # only (measured on B200 per call, fused / split: 4096 x 4096 T = 16 14.5 / 21.0 us, T = 32 22.4 / 23.7, T = 64
 # 46.3 / 29.2; 11008 x 4096 T = 16 30.1 / 34.0, T = 24 40.6 / 39.2, T = 64 117.6 / 55.9).
 FUSED_BASE_MAX_TOKENS = 16
+# Modules keep int8 operands for the reconstructed path once they have served a long input (see ADEKernelLinear._expanded).
+EXPAND_FOR_RECON = True
 
 # the seven linear modules of a LLaMA decoder layer (same list as src/adaptation.py:39-42)
 LINEAR_MODULE_NAMES = (
@@ -69,6 +71,7 @@ class ADEKernelLinear(nn.Module):
         for k in STORED_KEYS:
             self.register_buffer(f"p4_{k}", p4[k])
         self._p4 = None
+        self._x8 = None               # (uq pointer, (u8, v8)): expanded operands of the reconstruction, built on demand
         self._group = None            # (FusedADEGroup, index) once fuse_kernel_linears has grouped this module
 
     def _stored_form(self) -> dict:
@@ -78,9 +81,19 @@ class ADEKernelLinear(nn.Module):
             self._p4["M"], self._p4["N"], self._p4["r"] = self._dims
         return self._p4
 
+    def _expanded(self):
+        """int8 operands of the reconstruction kernel, built on the first long input and kept ((d_o + d_i) * r bytes;
+        EXPAND_FOR_RECON = False keeps the packed codes only and unpacks inside the kernel on every call)."""
+        p4 = self._stored_form()
+        if self._x8 is None or self._x8[0] != p4["uq"].data_ptr():
+            self._x8 = (p4["uq"].data_ptr(), expand_codes(p4))
+        return self._x8[1]
+
     def merged_weight(self) -> torch.Tensor:
         """bf16(W_b + U^ V^^T), one launch of the reconstruction kernel."""
-        return recon_int4(self._stored_form(), self.weight, self.group_size)
+        p4 = self._stored_form()
+        expanded = self._expanded() if EXPAND_FOR_RECON and p4["r"] <= 1024 else None
+        return recon_int4(p4, self.weight, self.group_size, expanded=expanded)
 
     def forward(self, x):
         """x (..., d_i) -> (..., d_o) in bfloat16."""

@@ -477,7 +477,7 @@ def run_ade(args):
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            W = kernels.recon_int4(m._stored_form(), m.weight)
+            W = m.merged_weight()             # the module's route: int8 operands expanded once at first use, kept
             if record:
                 e1.record()
                 recon_ev.append((e0, e1))
@@ -539,6 +539,16 @@ def run_ade(args):
     t_wall1 = time.perf_counter()
     ms = s0.elapsed_time(s1)
     recon_ms = sum(a.elapsed_time(b) for a, b in recon_ev) / len(recon_ev)
+    # for the record: the same launches with the codes unpacked inside the kernel on every call (no kept int8 operands)
+    pk = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for i in range(2 * len(mods) + 1):
+        if i == len(mods):
+            pk[0].record()
+        m = mods[i % len(mods)]
+        kernels.recon_int4(m._stored_form(), m.weight)
+    pk[1].record()
+    torch.cuda.synchronize()
+    recon_packed_us = pk[0].elapsed_time(pk[1]) * 1e3 / (len(mods) + 1)
 
     # ---- end to end through the module API, host buffers in and out
     for i in range(4):
@@ -624,7 +634,9 @@ def run_ade(args):
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": RECON_TRAFFIC_BYTES, "traffic_source": "ncu capture of `bench.py --case recon`, not this run",
-                         "peak_kind": peak_kind, "kernel": "recon_strip_kernel", "us_per_launch": recon_ms * 1e3,
+                         "peak_kind": peak_kind, "kernel": "recon_strip_kernel (int8 operands expanded once per module and kept; "
+                         "algorithmic bytes count the packed codes)", "us_per_launch": recon_ms * 1e3,
+                         "us_per_launch_unpacking_in_kernel": recon_packed_us,
                          "int8_tops_kernel_only": (WORK_OPS / 3) / (recon_ms * 1e-3) / 1e12},
             "cpu_baseline": {"value": cpu_tops, "unit": UNIT, "cores": cpu_threads, "blas_threads": blas, "kind": "port",
                              "sample": f"{cpu_rows} of 11008 rows of gate_proj: reconstruct + base add + x W'^T, median of 5, {cpu_sec:.2f} s per pass"},
@@ -642,7 +654,8 @@ def run_case(argv):
     """One small fixed workload of a single kernel (seeded random packed fields, no SVD, well under 1 GB on the
     device), a handful of launches: what a profiler capture of two or three launches is taken on.
 
-        python bench.py --case recon [M N r]          default 11008 4096 512 (Llama-2-7B gate_proj delta)
+        python bench.py --case recon [M N r [x]]      default 11008 4096 512 1 (Llama-2-7B gate_proj delta; x = 0: codes
+                                                      unpacked inside the kernel instead of int8 operands expanded beforehand)
         python bench.py --case factored [T M N r]     default 16 4096 4096 256 (q_proj delta)
         python bench.py --case decode                 one graph replay of the 7B-architecture decode step (launch list)
     """
@@ -653,14 +666,16 @@ def run_case(argv):
     what, nums = argv[0], [int(a) for a in argv[1:]]
     dev = "cuda"
     if what == "recon":
-        M, N, r = nums if len(nums) == 3 else (11008, 4096, 512)
+        M, N, r, expanded = nums if len(nums) == 4 else (*nums, 1) if len(nums) == 3 else (11008, 4096, 512, 1)
         p4 = kernels.pack_int4(synth.random_packed(M, N, r, 1), device=dev)
         W = synth.base_weight(M, N, 5).to(dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
+        x8 = kernels.expand_codes(p4) if expanded else None
         for _ in range(4):
-            kernels.recon_int4(p4, W, status=status)
+            kernels.recon_int4(p4, W, status=status, expanded=x8)
         torch.cuda.synchronize()
-        print(f"recon {M}x{N} r={r}: 4 launches, device status {int(status.item())}")
+        print(f"recon {M}x{N} r={r} ({'int8 operands' if expanded else 'codes unpacked in the kernel'}): 4 launches, "
+              f"device status {int(status.item())}")
     elif what == "factored":
         T, M, N, r = nums if len(nums) == 4 else (16, 4096, 4096, 256)
         p4 = kernels.pack_int4(synth.random_packed(M, N, r, 1), device=dev)

@@ -218,6 +218,23 @@ int ade_b200_recon(const ade_delta_t* d, const void* w_b, void* w_out,
                    int32_t* dbg_acc, int* status_dev, void* stream);
 
 /*
+ * Reconstructed application from expanded operands.  The reference's kernel unpacks the 4-bit codes and subtracts
+ * the zero-points inside its main loop (src/kernels.py:296-331); a module that serves many reconstructions can do
+ * that once instead:
+ *
+ *     ade_b200_expand_codes    writes u8 [M][r] and v8 [N][r] int8 = code - zero-point, in the order of the
+ *                              contraction the kernel uses (r bytes per row; (M + N) * r bytes in all);
+ *     ade_b200_recon_expanded  is ade_b200_recon reading those arrays by TMA straight into the operand tiles
+ *                              (no unpack role in the kernel); same arithmetic, bit-identical w_out and dbg_acc.
+ *
+ * d still supplies the scales (us, vs) and the shape; u8, v8 16-byte aligned.  Ranks above 1024 are served by
+ * ade_b200_recon (the arrays are then ignored).
+ */
+int ade_b200_expand_codes(const ade_delta_t* d, void* u8, void* v8, void* stream);
+int ade_b200_recon_expanded(const ade_delta_t* d, const void* u8, const void* v8, const void* w_b, void* w_out,
+                            int32_t* dbg_acc, int* status_dev, void* stream);
+
+/*
  * Elementwise pieces of a LLaMA decoder layer at decode sizes, one launch each.  No counterpart in the reference, which
  * leaves them to transformers (src/evaluate.py:241 calls model.generate): there an RMSNorm is eight elementwise
  * kernels, the rotary embedding fourteen, SiLU and product two, and inside a CUDA graph of the decode step they cost

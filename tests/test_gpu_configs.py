@@ -133,6 +133,10 @@ def test_config1_reconstructed_mlp(name, M, N):
     out0 = kernels.recon_int4(p4, torch.zeros_like(Wd))
     diff = (out.float() - out0.float() - Wd.float()).abs().max().item()
     assert diff <= 2.0 ** -8 * float(out.float().abs().max())
+    # the module's own route: int8 operands expanded once and kept, kernel fed by TMA; same bits
+    assert torch.equal(lin.merged_weight(), out) and lin._x8 is not None
+    kept = lin._x8[1][0].data_ptr()
+    assert torch.equal(lin.merged_weight(), out) and lin._x8[1][0].data_ptr() == kept
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -226,6 +230,11 @@ def test_reconstruction_13b_shapes_bit_exact(M, N, r):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert torch.equal(out, merged_t)
+    out_x = kernels.recon_int4(p4, Wd, status=status, expanded=kernels.expand_codes(p4))   # and from int8 operands
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(out_x, merged_t)
+    del out_x
     for g0 in range(0, ng, 2):                              # accumulators two groups at a time (memory)
         g1 = min(g0 + 2, ng)
         sub = {k: (v[:, g0 * 128:g1 * 128] if k == "U_codes" else v[g0 * 128:g1 * 128] if k == "Vt_codes"

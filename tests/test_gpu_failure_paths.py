@@ -50,25 +50,28 @@ def test_factored_wait_for_h_expires_and_recovers(T, fused, silent_producers):
     assert kernels.factored_status(DEV, T, r) == 0 and torch.equal(again, good)
 
 
-@pytest.mark.parametrize("r,codes", [(256, {1, 2, 3, 4, 5, 8, 9}), (640, {1, 2, 3, 4, 5, 8, 9}), (1152, {1, 3})])
-def test_reconstruction_waits_expire_and_recover(r, codes, silent_producers):
-    """Both configurations of the strip-resident kernel and the general kernel: without code loads the first waiting
-    role records its ADE_DEV_TIMEOUT_* code, every role runs to its end, tensor memory is released."""
+@pytest.mark.parametrize("r,codes,expanded", [(256, {1, 2, 3, 4, 5, 8, 9}, False), (640, {1, 2, 3, 4, 5, 8, 9}, False),
+                                              (1152, {1, 3}, False), (256, {1, 3, 9}, True), (640, {1, 3, 9}, True)])
+def test_reconstruction_waits_expire_and_recover(r, codes, expanded, silent_producers):
+    """Both configurations of the strip-resident kernel (with packed and with expanded operands) and the general
+    kernel: without code loads the first waiting role records its ADE_DEV_TIMEOUT_* code, every role runs to its
+    end, tensor memory is released."""
     M, N = 384, 512
     p4 = kernels.pack_int4(synth.random_packed(M, N, r, 8), device=DEV)
     W = synth.base_weight(M, N, 9).to(DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     _lib.set_option(_lib.OPT_DROP_SIGNALS, 0)
-    good = kernels.recon_int4(p4, W, status=status)
+    x8 = kernels.expand_codes(p4) if expanded else None
+    good = kernels.recon_int4(p4, W, status=status, expanded=x8)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     _lib.set_option(_lib.OPT_DROP_SIGNALS, 1)
-    kernels.recon_int4(p4, W, status=status)
+    kernels.recon_int4(p4, W, status=status, expanded=x8)
     torch.cuda.synchronize()
     code = int(status.item())
     assert code in codes, _lib.DEVICE_STATUS.get(code, code)
     _lib.set_option(_lib.OPT_DROP_SIGNALS, 0)
     status.zero_()
-    again = kernels.recon_int4(p4, W, status=status)
+    again = kernels.recon_int4(p4, W, status=status, expanded=x8)
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and torch.equal(again, good)

@@ -48,14 +48,15 @@ def _random_case(M, N, r, T, seed):
     }
 
 
-def _run_recon(case, dbg=True):
+def _run_recon(case, dbg=True, expanded=False):
     tp = case.get("tpacked") or _torch_packed(case["packed"])
     p4 = kernels.pack_int4(tp, device=DEV)
+    x8 = kernels.expand_codes(p4) if expanded else None
     base = _bf16(case["W_b"]).to(DEV)
     ng = case["r"] // 128
     acc = torch.full((ng, case["M"], case["N"]), -7, dtype=torch.int32, device=DEV) if dbg else None
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    out = kernels.recon_int4(p4, base, dbg_acc=acc, status=status)
+    out = kernels.recon_int4(p4, base, dbg_acc=acc, status=status, expanded=x8)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, _lib.DEVICE_STATUS.get(int(status.item()))
     return out, acc
@@ -91,6 +92,8 @@ def test_recon_golden_bit_exact(path):
     assert np.array_equal(_bits(out), merged), "merged weight differs from the reference arithmetic"
     out2, _ = _run_recon(case, dbg=False)                  # the production instantiation
     assert torch.equal(out, out2)
+    out3, acc3 = _run_recon(case, expanded=True)           # the same from expanded int8 operands
+    assert torch.equal(out, out3) and torch.equal(acc, acc3)
 
 
 @pytest.mark.parametrize("M,N,r", [(128, 128, 128), (256, 384, 256), (192, 128, 384), (100, 256, 512),
@@ -107,6 +110,28 @@ def test_recon_shapes_bit_exact(M, N, r):
     assert np.array_equal(_bits(out), merged)
     out2, _ = _run_recon(case, dbg=False)
     assert torch.equal(out, out2)
+    # expanded int8 operands (TMA-fed kernel without an unpack role; ranks above 1024 ignore them): identical bits
+    out3, acc3 = _run_recon(case, expanded=True)
+    assert torch.equal(out, out3) and torch.equal(acc, acc3)
+    out4, _ = _run_recon(case, dbg=False, expanded=True)
+    assert torch.equal(out, out4)
+
+
+def test_expand_codes_layout():
+    """u8 / v8 hold code minus zero-point; inside every 8 consecutive ranks the order is that of the stored nibbles
+    (low nibbles of the word's four bytes, then the high ones): position j holds code (0, 4, 1, 5, 2, 6, 3, 7)[j]."""
+    M, N, r = 200, 256, 384
+    tp = synth.random_packed(M, N, r, 5)
+    p4 = kernels.pack_int4(tp, device=DEV)
+    u8, v8 = kernels.expand_codes(p4)
+    torch.cuda.synchronize()
+    assert u8.dtype == torch.int8 and tuple(u8.shape) == (M, r) and tuple(v8.shape) == (N, r)
+    perm = torch.tensor([0, 4, 1, 5, 2, 6, 3, 7])
+    uc = tp["U_codes"].to(torch.int16) - tp["U_zero"].to(torch.float32).to(torch.int16).repeat_interleave(128, dim=1)
+    vc = (tp["Vt_codes"].to(torch.int16) - tp["Vt_zero"].to(torch.float32).to(torch.int16).repeat_interleave(128, dim=0)).t()
+    for got, want in ((u8, uc), (v8, vc)):
+        want = want.reshape(want.shape[0], r // 8, 8)[..., perm].reshape(want.shape[0], r)
+        assert torch.equal(got.cpu().to(torch.int16), want)
 
 
 def _check_factored(case, fused):

@@ -114,7 +114,8 @@ def test_torch_binding_loads_and_registers_its_operators():
     """The thin torch binding (libade_b200_torch.so) loads without a GPU and registers the two hot entry points."""
     ops = _lib.ops()
     assert str(ops.factored.default._schema).startswith("ade_b200::factored(Tensor x, Tensor? weight, Tensor? y_dense, Tensor uq")
-    assert "Tensor? dbg_acc, Tensor? status) -> Tensor" in str(ops.recon.default._schema)
+    assert "Tensor? dbg_acc, Tensor? status, Tensor? u8, Tensor? v8) -> Tensor" in str(ops.recon.default._schema)
+    assert str(ops.expand.default._schema).endswith("-> (Tensor, Tensor)")
     with pytest.raises((RuntimeError, NotImplementedError)):           # CPU tensors: no CPU kernel is registered
         ops.recon(torch.zeros(128, 128, dtype=torch.bfloat16), *[torch.zeros(1, dtype=torch.uint8)] * 7, 128, 128, 128, None, None)
 
