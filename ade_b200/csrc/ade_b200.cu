@@ -72,7 +72,8 @@ int device_info(const DeviceInfo** out) {
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
                 !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
-                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) ||
+                !cuda_ok(cudaFuncSetAttribute(ade::recon_strip_kernel<false, false, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
                 return ADE_ERR_CUDA;
             if (!cuda_ok(cudaFuncSetAttribute(ade::compress_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               static_cast<int>(ade::compress_smem_bytes(ade::CQ_MAX_RANK, true)))))
@@ -659,6 +660,7 @@ static int recon_impl(const ade_delta_t* d, const void* u8, const void* v8, cons
                 else ade::recon_strip_kernel<false, true, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
             } else {
                 if (dbg_acc) ade::recon_strip_kernel<true, false, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
+                else if (ng == 4) ade::recon_strip_kernel<false, false, true, 4><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
                 else ade::recon_strip_kernel<false, false, true><<<grid, ade::RS_THREADS_EXP, smem, st>>>(p, maps);
             }
             return cuda_ok(cudaGetLastError()) ? ADE_OK : ADE_ERR_CUDA;

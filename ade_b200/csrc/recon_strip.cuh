@@ -66,7 +66,8 @@ template <bool BIG, bool EXP = false>
 struct RsCfg {
     static constexpr int GROUPS = BIG ? 8 : 4;           // resident groups at most
     static constexpr int B_STAGES = EXP ? (BIG ? 3 : 5) : (BIG ? 2 : 3);   // int8 V tiles in flight
-    static constexpr int RAW_DEPTH = EXP ? 0 : (BIG ? 2 : 4);                // packed items in flight
+    static constexpr int RAW_DEPTH = EXP ? 1 : (BIG ? 2 : 4);                // packed items in flight (no ring when EXP)
+    static constexpr int RAW_BYTES = EXP ? 0 : RAW_DEPTH * RS_RAW_SLOT;
     static constexpr int WB_BUFS = BIG ? 1 : 2;          // box buffers per epilogue warp
     static constexpr int WB_BYTES = RS_EPI_WARPS * WB_BUFS * RS_BOX_BYTES;
     // barrier indices (8 bytes each)
@@ -77,14 +78,19 @@ struct RsCfg {
     static constexpr int BAR_A_FULL = BAR_B_EMPTY + B_STAGES;
     static constexpr int BAR_A_FREE = BAR_A_FULL + GROUPS;
     static constexpr int BAR_TFULL = BAR_A_FREE + 1;
-    static constexpr int BAR_TEMPTY = BAR_TFULL + RS_ACC_STAGES;
+    // Accumulators ready: with at most four groups a tile fits the four stages, and the issuer reports a whole tile
+    // at once (barrier tile % 8: up to five tiles of a one-group delta are in flight); with more groups than stages
+    // it reports every group (barrier = stage).
+    static constexpr bool PER_TILE = EXP && !BIG;
+    static constexpr int TFULL_BARS = 8;
+    static constexpr int BAR_TEMPTY = BAR_TFULL + TFULL_BARS;
     static constexpr int BAR_SC_FULL = BAR_TEMPTY + RS_ACC_STAGES;
     static constexpr int BAR_SC_EMPTY = BAR_SC_FULL + 2;
     static constexpr int BAR_WB = BAR_SC_EMPTY + 2;
     static constexpr int BAR_COUNT = BAR_WB + WB_BUFS * RS_EPI_WARPS;
     __host__ __device__ static constexpr size_t smem_bytes(int ng) {
         return 1024 /* alignment slack */ + static_cast<size_t>(ng) * RS_OPER_BYTES + static_cast<size_t>(B_STAGES) * RS_OPER_BYTES +
-               WB_BYTES + static_cast<size_t>(RAW_DEPTH) * RS_RAW_SLOT + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + BAR_COUNT * 8 + 16;
+               WB_BYTES + RAW_BYTES + static_cast<size_t>(ng) * RS_SC_BYTES * 2 + BAR_COUNT * 8 + 16;
     }
 };
 
@@ -144,7 +150,9 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const uint8_t* __rest
     }
 }
 
-template <bool DBG, bool BIG, bool EXP = false>
+// NG > 0: the number of groups is fixed at compile time (4: rank 512), so the epilogue's group loop unrolls with
+// constant stage, table and tensor-memory offsets; 0: read from the delta.
+template <bool DBG, bool BIG, bool EXP = false, int NG = 0>
 __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_strip_kernel(const ReconParams p, const __grid_constant__ ReconMaps maps) {
     using C = RsCfg<BIG, EXP>;
     constexpr int MMA_WARP = EXP ? RS_EPI_WARPS : RS_MMA_WARP;
@@ -153,12 +161,12 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
     const uint32_t base = (raw0 + 1023u) & ~1023u;
-    const int ng = p.r >> 7;
+    const int ng = NG > 0 ? NG : (p.r >> 7);
     const uint32_t a_res = base;                                          // [ng][128][128] int8, resident strip of U
     const uint32_t b_st = a_res + ng * RS_OPER_BYTES;                     // [C::B_STAGES][128][128] int8
     const uint32_t wbuf = b_st + C::B_STAGES * RS_OPER_BYTES;             // [16 warps][2][32][64 B]
     const uint32_t rawr = wbuf + C::WB_BYTES;                             // [C::RAW_DEPTH][RS_RAW_SLOT]
-    const uint32_t scf = rawr + C::RAW_DEPTH * RS_RAW_SLOT;               // [2][ng][RS_SC_BYTES] scale tables
+    const uint32_t scf = rawr + C::RAW_BYTES;                             // [2][ng][RS_SC_BYTES] scale tables
     const uint32_t bars = scf + ng * RS_SC_BYTES * 2;
     uint8_t* gen = smem_raw + (bars - raw0);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_COUNT * 8);
@@ -177,10 +185,8 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
         }
         for (int i = 0; i < C::GROUPS; ++i) mbar_init(bar(C::BAR_A_FULL + i), EXP ? 1 : 4);
         mbar_init(bar(C::BAR_A_FREE), 1);
-        for (int i = 0; i < RS_ACC_STAGES; ++i) {
-            mbar_init(bar(C::BAR_TFULL + i), 1);
-            mbar_init(bar(C::BAR_TEMPTY + i), RS_EPI_WARPS);
-        }
+        for (int i = 0; i < C::TFULL_BARS; ++i) mbar_init(bar(C::BAR_TFULL + i), 1);
+        for (int i = 0; i < RS_ACC_STAGES; ++i) mbar_init(bar(C::BAR_TEMPTY + i), RS_EPI_WARPS);
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(C::BAR_SC_FULL + i), 1);
             mbar_init(bar(C::BAR_SC_EMPTY + i), RS_EPI_WARPS);
@@ -258,7 +264,20 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
                 mbar_arrive_expect_tx(wbar, RS_BOX_BYTES);
                 tma_load_2d(box, &maps.wb, n0 + hh * 32, m0 + q * 32, wbar);
             }
-            wait_bounded(bar(C::BAR_SC_FULL + b), jph, wctx, 5);
+            // A wait costs a few hundred cycles of this warp's time even when the phase completed long ago (a round
+            // trip through shared memory and a branch, at this warp's share of the issue slots), so what a tile needs
+            // is tested together, three tests in flight: scale tables, accumulators of the whole tile, base box
+            // (requested a tile ago).  Only what is not there yet is waited for.
+            const uint32_t tfb = bar(C::BAR_TFULL + (j & (C::TFULL_BARS - 1))), tfph = (j / C::TFULL_BARS) & 1;
+            {
+                const bool ok_sc = mbar_test(bar(C::BAR_SC_FULL + b), jph);
+                const bool ok_tf = C::PER_TILE ? mbar_test(tfb, tfph) : true;
+                const bool ok_wb = C::WB_BUFS == 2 ? mbar_test(wbar, wph) : true;
+                if (!ok_sc) wait_bounded(bar(C::BAR_SC_FULL + b), jph, wctx, 5);
+                if (!ok_tf) wait_bounded(tfb, tfph, wctx, 3);
+                if (!ok_wb) wait_bounded(wbar, wph, wctx, 6);
+            }
+            if (C::PER_TILE) tc_fence_after();
             EPI_STAMP(0x0200 | (j & 255));
             const uint32_t sct = scf + b * (ng * RS_SC_BYTES);          // this tile's tables
 
@@ -267,11 +286,16 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
             for (int i = 0; i < 16; ++i) acc[i] = 0ull;
             const uint64_t one2 = f2_pack(p.one, p.one);  // 1.0f from the kernel parameters: acc + t as fma(t, 1, acc), never contracted
 
+            // (Requesting the next 16-column chunk from tensor memory before rescaling the current one, across groups
+            // too, was measured with the expanded operands: 61.8 us against 58.5 without.)
+#pragma unroll(NG > 0 ? NG : 1)
             for (int g = 0; g < ng; ++g, ++it) {
-                const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
+                const uint32_t a = NG == RS_ACC_STAGES ? g : it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
+                if (!C::PER_TILE) {
+                    wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
+                    tc_fence_after();
+                }
                 EPI_STAMP(0x0300 | g);
-                tc_fence_after();
                 const uint32_t scg = sct + g * RS_SC_BYTES;
                 const float u = __uint_as_float(lds4(scg + row * 4));
                 const uint64_t uu = f2_pack(u, u);
@@ -282,13 +306,7 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
                 // The accumulator started at RC_MAGIC, so its bits are the float m + P, exactly.
                 // x = fma(m + P, us, -m us) = P us exactly (|P| < 2^15, us has 8 significant bits);
                 // t = x * vs is P * (us * vs) rounded once, as the reference rounds it; acc + t rounded once.
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
-                    tmem_ld16(tbase + ch * 16, vc);
-                    tmem_ld_wait();
-                    EPI_STAMP(0x0400 | (g << 1) | ch);
-                    tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
+                auto rescale16 = [&](const uint32_t (&vc)[16], const int ch) {
 #pragma unroll
                     for (int h4 = 0; h4 < 2; ++h4) {
                         uint64_t vs2[4];                 // vs of 8 columns as packed pairs, both loads in flight together
@@ -308,6 +326,15 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
                             *reinterpret_cast<int4*>(d + i) = make_int4(vc[i] - RC_MAGIC, vc[i + 1] - RC_MAGIC, vc[i + 2] - RC_MAGIC,
                                                                         vc[i + 3] - RC_MAGIC);
                     }
+                };
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
+                    tmem_ld16(tbase + ch * 16, vc);
+                    tmem_ld_wait();
+                    EPI_STAMP(0x0400 | (g << 1) | ch);
+                    tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
+                    rescale16(vc, ch);
                 }
                 EPI_STAMP(0x0500 | g);
                 tmem_st_wait();                          // accumulator stage re-armed: hand it back
@@ -328,7 +355,7 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::BAR_SC_EMPTY + b));             // this warp is done with the scale tables
             EPI_STAMP(0x0700 | (j & 255));
-            wait_bounded(wbar, wph, wctx, 6);
+            if (C::WB_BUFS == 1) wait_bounded(wbar, wph, wctx, 6);
             EPI_STAMP(0x0800 | (j & 255));
             uint4 wv4[4];                                // 8 columns per 16-byte chunk
 #pragma unroll
@@ -439,35 +466,50 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
     } else {
     if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
+        // With expanded operands the whole warp walks the loop and waits and one elected lane issues: the loop stays
+        // warp-uniform, so its counters, barrier addresses and descriptors can live in uniform registers (431 instead
+        // of 648 cycles per group for the four MMAs and their commits).  With the unpack role present a single thread
+        // runs the loop (the other form was slower there).
         // (two issuing threads taking alternate groups were tried with the expanded operands: no faster)
-        if (lane == 0) {
+        if (EXP || lane == 0) {
             uint32_t it = 0, k = 0, s = 0, bph = 0;
 #ifdef ADE_TRACE
             int tcn = 0;
+#define MMA_STAMP(code) do { if (lane == 0) ADE_TRACE_STAMP(p, tcn, 3, code); } while (0)
+#else
+#define MMA_STAMP(code) do { } while (0)
 #endif
             int nt = nt0;
-            for (int tile = t_begin; tile < t_end; ++tile) {
+            uint32_t jt = 0;
+            for (int tile = t_begin; tile < t_end; ++tile, ++jt) {
                 const bool first = tile == t_begin || nt == 0;
                 const bool last = tile == t_end - 1 || nt + 1 == tiles_n;
                 if (++nt == tiles_n) nt = 0;
                 for (int g = 0; g < ng; ++g, ++it) {
                     const uint32_t a = it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
-                    ADE_TRACE_STAMP(p, tcn, 3, 0x2000 | g);
-                    wait_bounded(bar(C::BAR_TEMPTY + a), aph, wctx, 4);
-                    ADE_TRACE_STAMP(p, tcn, 3, 0x2100 | g);
-                    wait_bounded(bar(C::BAR_B_FULL + s), bph, wctx, 1);
-                    ADE_TRACE_STAMP(p, tcn, 3, 0x2200 | g);
+                    MMA_STAMP(0x2000 | g);
+                    {
+                        const bool ok_e = mbar_test(bar(C::BAR_TEMPTY + a), aph), ok_b = mbar_test(bar(C::BAR_B_FULL + s), bph);
+                        if (!ok_e) wait_bounded(bar(C::BAR_TEMPTY + a), aph, wctx, 4);
+                        MMA_STAMP(0x2100 | g);
+                        if (!ok_b) wait_bounded(bar(C::BAR_B_FULL + s), bph, wctx, 1);
+                    }
+                    MMA_STAMP(0x2200 | g);
                     if (first) wait_bounded(bar(C::BAR_A_FULL + g), k & 1, wctx, 9);
                     tc_fence_after();
                     const uint64_t ad = smem_desc_k_sw128(a_res + g * RS_OPER_BYTES);
                     const uint64_t bd = smem_desc_k_sw128(b_st + s * RS_OPER_BYTES);
+                    if (!EXP || elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * kk, bd + 2 * kk, RC_IDESC, 1u);
-                    tc_commit(bar(C::BAR_B_EMPTY + s));
-                    tc_commit(bar(C::BAR_TFULL + a));
-                    if (last && g == ng - 1) tc_commit(bar(C::BAR_A_FREE));    // the strip of U may be overwritten
-                    ADE_TRACE_STAMP(p, tcn, 3, 0x2300 | g);
+                        for (int kk = 0; kk < 4; ++kk)
+                            tc_mma_i8(tmem_base + a * RC_TILE, ad + 2 * kk, bd + 2 * kk, RC_IDESC, 1u);
+                        tc_commit(bar(C::BAR_B_EMPTY + s));
+                        if (!C::PER_TILE) tc_commit(bar(C::BAR_TFULL + a));
+                        else if (g == ng - 1) tc_commit(bar(C::BAR_TFULL + (jt & (C::TFULL_BARS - 1))));
+                        if (last && g == ng - 1) tc_commit(bar(C::BAR_A_FREE));    // the strip of U may be overwritten
+                    }
+                    if (EXP) __syncwarp();
+                    MMA_STAMP(0x2300 | g);
                     if (++s == C::B_STAGES) {
                         s = 0;
                         bph ^= 1;
