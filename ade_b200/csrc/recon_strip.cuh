@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
         }
 
         uint32_t it = 0;
+        bool tf_ready = false;                            // per-group barriers: the coming group's accumulator was seen complete
         int j = 0, sm = strip0, nt = nt0;
 #ifdef ADE_TRACE
         int tcn = 0;
@@ -292,7 +293,9 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
             for (int g = 0; g < ng; ++g, ++it) {
                 const uint32_t a = NG == RS_ACC_STAGES ? g : it % RS_ACC_STAGES, aph = (it / RS_ACC_STAGES) & 1;
                 if (!C::PER_TILE) {
-                    wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
+                    // the barrier of this group was tested while the previous group was being rescaled (a completed phase
+                    // stays completed): the round trip of a wait is off the chain unless the accumulator really is late
+                    if (!tf_ready) wait_bounded(bar(C::BAR_TFULL + a), aph, wctx, 3);
                     tc_fence_after();
                 }
                 EPI_STAMP(0x0300 | g);
@@ -331,6 +334,10 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
                 for (int ch = 0; ch < 2; ++ch) {
                     uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
                     tmem_ld16(tbase + ch * 16, vc);
+                    if (!C::PER_TILE && ch == 0) {       // under the load: is the next group's accumulator (next stage) there yet?
+                        const uint32_t a1 = (it + 1) % RS_ACC_STAGES, ph1 = ((it + 1) / RS_ACC_STAGES) & 1;
+                        tf_ready = mbar_test(bar(C::BAR_TFULL + a1), ph1);
+                    }
                     tmem_ld_wait();
                     EPI_STAMP(0x0400 | (g << 1) | ch);
                     tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
