@@ -228,6 +228,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* _
                 for (int d = 0; d < hd; ++d) a += qs[d] * kn[d];
             } else {
                 const uint4* row = reinterpret_cast<const uint4*>(kcb + static_cast<size_t>(p) * hd);
+#pragma unroll 8
                 for (int c8 = 0; c8 < (hd >> 3); ++c8) {
                     const uint4 w = row[c8];
                     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* _
     sum = red[0] + red[1] + red[2] + red[3];
     __syncthreads();
     // weighted sum of v: a thread owns 8 consecutive dimensions (one 16-byte piece of a cache row) and every
-    // (128 / (hd / 8))-th position, eight rows in flight at a time; the position lanes are summed through shared memory
+    // (128 / (hd / 8))-th position, up to sixteen rows in flight at a time; the position lanes are summed through shared
+    // memory
     const int chunks = hd >> 3;                            // 16-byte pieces per row: 4 .. 32
     const int lanes_p = 128 / chunks;                      // position lanes: 32 .. 4
     const int c8 = tid % chunks, pl = tid / chunks;
@@ -287,6 +289,18 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __nv_bfloat16* _
         const uint4* vrow = reinterpret_cast<const uint4*>(vcb) + c8;
         const int stride = chunks;                         // uint4 per row
         int p = pl;
+        for (; p + 15 * lanes_p < hi; p += 16 * lanes_p) {     // long caches: sixteen rows in flight
+            uint4 w4[16];
+            float wt[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int pp = p + u * lanes_p;
+                wt[u] = pp == p0 ? 0.f : sc[pp];
+                w4[u] = vrow[static_cast<size_t>(pp) * stride];
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) add_row(w4[u], wt[u]);
+        }
         for (; p + 7 * lanes_p < hi; p += 8 * lanes_p) {
             uint4 w4[8];
             float wt[8];
