@@ -36,7 +36,7 @@ DEVICE_STATUS = {
     11: "ADE_DEV_TIMEOUT_SCALES_FREE: scale warp gave up waiting for a free table buffer",
 }
 # ade_b200_set_option
-OPT_WAIT_LIMIT_CYCLES, OPT_COOPERATIVE_LAUNCH, OPT_DROP_SIGNALS = 1, 2, 3
+OPT_WAIT_LIMIT_CYCLES, OPT_COOPERATIVE_LAUNCH, OPT_DROP_SIGNALS, OPT_ATTN_SINGLE_PASS = 1, 2, 3, 4
 
 # every symbol include/ade_b200.h declares
 EXPORTS = (

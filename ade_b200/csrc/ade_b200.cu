@@ -42,6 +42,7 @@ DeviceInfo g_dev[kMaxDevices];
 long long g_wait_limit = ade::RC_SPIN_LIMIT;   // clock cycles a device-side wait may take before it gives up
 int g_cooperative = 1;                         // factored kernel launched cooperatively (co-residency guaranteed)
 int g_drop_signals = 0;                        // diagnostic: producers inside the kernels stay silent
+int g_attn_single_pass = 1;                    // attention step: the single-pass kernel where the head dimension allows it
 #ifdef ADE_TRACE
 unsigned long long* g_trace = nullptr;         // development builds: device buffer for event stamps (option 100)
 #endif
@@ -529,6 +530,22 @@ int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void
     if (B < 1 || q_heads < 1 || k_heads < 1 || q_heads % k_heads || cache_len < 1) return ADE_ERR_SHAPE;
     if (head_dim < 32 || head_dim > 256 || head_dim % 32) return ADE_ERR_SHAPE;
     if (!aligned16(k_cache) || !aligned16(v_cache)) return ADE_ERR_ALIGN;
+    if (g_attn_single_pass) {
+        // head dimensions 32 / 64 / 128 / 256: one streaming pass over the cache (any cache length)
+        const __nv_bfloat16 *qp = static_cast<const __nv_bfloat16*>(q), *kp = static_cast<const __nv_bfloat16*>(k),
+                            *vp = static_cast<const __nv_bfloat16*>(v), *cp = static_cast<const __nv_bfloat16*>(cos_t),
+                            *sp = static_cast<const __nv_bfloat16*>(sin_t);
+        __nv_bfloat16 *kcp = static_cast<__nv_bfloat16*>(k_cache), *vcp = static_cast<__nv_bfloat16*>(v_cache), *op = static_cast<__nv_bfloat16*>(out);
+        const bool* mp = static_cast<const bool*>(mask);
+#define ADE_ATTN_STREAM(CH)                                                                                                       \
+    return launch_small(ade::attn_decode_stream_kernel<CH>, B * q_heads, 128, 0, stream, qp, kp, vp, cp, sp, mp, kcp, vcp, pos, ticket, op, \
+                        q_heads, k_heads, cache_len, q_row_stride, k_row_stride, v_row_stride, cs_batch_stride, mask_row_stride, scale)
+        if (head_dim == 32) ADE_ATTN_STREAM(4);
+        if (head_dim == 64) ADE_ATTN_STREAM(8);
+        if (head_dim == 128) ADE_ATTN_STREAM(16);
+        if (head_dim == 256) ADE_ATTN_STREAM(32);
+#undef ADE_ATTN_STREAM
+    }
     const size_t smem = (static_cast<size_t>(7) * head_dim + cache_len) * sizeof(float);
     if (smem > 48 * 1024) return ADE_ERR_SHAPE;                           // cache lengths up to about 10 000 positions
     return launch_small(ade::attn_decode_kernel, B * q_heads, 128, smem, stream, static_cast<const __nv_bfloat16*>(q),
@@ -560,6 +577,9 @@ int ade_b200_set_option(int option, long long value) {
             return ADE_OK;
         case ADE_OPT_DROP_SIGNALS:
             g_drop_signals = value != 0;
+            return ADE_OK;
+        case ADE_OPT_ATTN_SINGLE_PASS:
+            g_attn_single_pass = value != 0;
             return ADE_OK;
 #ifdef ADE_TRACE
         case 100:

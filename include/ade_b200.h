@@ -281,11 +281,14 @@ int ade_b200_attn_decode(const void* q, const void* k, const void* v, const void
  *                               issue no code loads), so every wait that depends on them runs into the limit
  *                               above: the way to exercise the time-out path without any fault.  Outputs of
  *                               such calls are undefined.
+ *   ADE_OPT_ATTN_SINGLE_PASS    1 (default): ade_b200_attn_decode walks the cache once with a running softmax when the
+ *                               head dimension is 32, 64, 128 or 256; 0: always the two-pass kernel.
  * Returns ADE_OK, or ADE_ERR_SHAPE for an unknown option or a negative limit.
  */
 #define ADE_OPT_WAIT_LIMIT_CYCLES 1
 #define ADE_OPT_COOPERATIVE_LAUNCH 2
 #define ADE_OPT_DROP_SIGNALS 3
+#define ADE_OPT_ATTN_SINGLE_PASS 4
 int ade_b200_set_option(int option, long long value);
 
 #ifdef __cplusplus

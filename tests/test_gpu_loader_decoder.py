@@ -183,8 +183,15 @@ def test_attention_decode_step_against_torch():
 
     from ade_b200 import decode_ops
 
+    from ade_b200 import _lib
+
     g = torch.Generator().manual_seed(7)
-    for B, hq, hk, hd, L, start in [(1, 32, 32, 128, 193, 64), (3, 8, 2, 64, 40, 5), (2, 40, 40, 128, 64, 0)]:
+    # head dimensions 64 / 128 / 32 take the single-pass kernel (and, with the option off, the two-pass one); 96 only has
+    # the two-pass kernel; the long cache makes every row group walk several batches of rows
+    cases = [(1, 32, 32, 128, 193, 64), (3, 8, 2, 64, 40, 5), (2, 40, 40, 128, 64, 0), (2, 8, 4, 128, 700, 640), (2, 4, 4, 96, 50, 10),
+             (1, 4, 2, 32, 300, 200)]
+    for single_pass, (B, hq, hk, hd, L, start) in [(sp, c) for sp in (1, 0) for c in cases]:
+        _lib.set_option(_lib.OPT_ATTN_SINGLE_PASS, single_pass)
         keys = torch.zeros(B, hk, L, hd, dtype=torch.bfloat16, device=DEV)
         vals = torch.zeros_like(keys)
         if start:
@@ -216,3 +223,4 @@ def test_attention_decode_step_against_torch():
             assert int(layer.cumulative_length) == pos + 1 and int(layer._ade_ticket) == 0     # advanced by the launch itself
             assert torch.equal(keys, rk) and torch.equal(vals, rv)                                  # cache written exactly
             assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
+    _lib.set_option(_lib.OPT_ATTN_SINGLE_PASS, 1)
