@@ -494,7 +494,10 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
             const int col = (warp + FA_WARPS * ((qi + static_cast<int>(blockIdx.x)) % cnt)) * 64 + tig * 8;   // rotated as in wx_block
             const int blk = row0 + qb * FA_ROWS;
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int mt = 0; mt < 2; ++mt) {
+                // the slice's last block may hold 16 rows or fewer (5120 rows over 148 CTAs are 34.6 each): its second
+                // m16 tile is then neither copied nor multiplied (skipping single eight-row halves as well was slower)
+                if (mt == 1 && blk + 16 >= row1) break;
 #pragma unroll
                 for (int hr = 0; hr < 2; ++hr) {
                     const int m = min(blk + mt * 16 + hr * 8 + gid, row1 - 1);     // rows past the slice: re-read the last one
@@ -502,6 +505,7 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
                     fa_cp_async16(sb + (mt * 4 + hr * 2) * STR, src);
                     fa_cp_async16(sb + (mt * 4 + hr * 2 + 1) * STR, src + 32);
                 }
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 // lanes whose token does not exist copy nothing (zero fill): eight lanes asking for the same
@@ -523,6 +527,7 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
     for (int b = 0; b < nb; ++b) {
         float acc[2][NT][4];
         zero_acc<NT>(acc);
+        const bool tile1 = row0 + b * FA_ROWS + 16 < row1;  // the block's second m16 tile holds rows of the slice
         for (int i = 0; i < cnt; ++i, ++q) {
             fa_cp_async_wait(S - 2);                        // item q has landed
             uint4 A[2][2][2];
@@ -532,7 +537,8 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
 #pragma unroll
                 for (int hr = 0; hr < 2; ++hr)
 #pragma unroll
-                    for (int s2 = 0; s2 < 2; ++s2) A[mt][hr][s2] = slot[(mt * 4 + hr * 2 + s2) * FA_THREADS];
+                    for (int s2 = 0; s2 < 2; ++s2)
+                        A[mt][hr][s2] = (mt == 0 || tile1) ? slot[(mt * 4 + hr * 2 + s2) * FA_THREADS] : make_uint4(0u, 0u, 0u, 0u);
             uint4 X[NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
@@ -548,6 +554,7 @@ __device__ __forceinline__ void wx_stream(const FactoredParams& p, float (*red)[
                     if (!live) xq = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
+                        if (mt == 1 && !tile1) break;
                         mma_bf16(acc[mt][nt], A[mt][0][s2].x, A[mt][1][s2].x, A[mt][0][s2].y, A[mt][1][s2].y, xq.x, xq.y);
                         mma_bf16(acc[mt][nt], A[mt][0][s2].z, A[mt][1][s2].z, A[mt][0][s2].w, A[mt][1][s2].w, xq.z, xq.w);
                     }
