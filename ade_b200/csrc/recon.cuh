@@ -309,12 +309,11 @@ __global__ void __launch_bounds__(RC_THREADS, 1) recon_kernel(const ReconParams 
                 const uint64_t uu = f2_pack(u, u);
                 const uint32_t tbase = lane_addr + a * RC_TILE;
                 const ulonglong2* svp = reinterpret_cast<const ulonglong2*>(sv + g * RC_TILE + hh * RC_CW);
-                // all of this thread's columns of the group in one go: both loads in flight together, then the
-                // columns are re-armed and the accumulator stage is handed back before any arithmetic
+                // all of this thread's columns of the group, then the columns are re-armed and the accumulator stage is
+                // handed back before any arithmetic
                 uint32_t v[RC_CW / 16][16];
 #pragma unroll
-                for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_ld16(tbase + ch * 16, v[ch]);
-                tmem_ld_wait();
+                for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_ld16_sync(tbase + ch * 16, v[ch]);
 #pragma unroll
                 for (int ch = 0; ch < RC_CW / 16; ++ch) tmem_st16_fill(tbase + ch * 16, magic4);
                 tmem_st_wait();

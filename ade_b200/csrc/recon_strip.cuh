@@ -333,12 +333,11 @@ __global__ void __launch_bounds__(EXP ? RS_THREADS_EXP : RS_THREADS, 1) recon_st
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint32_t vc[16];                     // 16 columns at a time: 32 would not fit the register budget
-                    tmem_ld16(tbase + ch * 16, vc);
-                    if (!C::PER_TILE && ch == 0) {       // under the load: is the next group's accumulator (next stage) there yet?
+                    if (!C::PER_TILE && ch == 0) {       // is the next group's accumulator (next stage) there yet?  Used a group later.
                         const uint32_t a1 = (it + 1) % RS_ACC_STAGES, ph1 = ((it + 1) / RS_ACC_STAGES) & 1;
                         tf_ready = mbar_test(bar(C::BAR_TFULL + a1), ph1);
                     }
-                    tmem_ld_wait();
+                    tmem_ld16_sync(tbase + ch * 16, vc);
                     EPI_STAMP(0x0400 | (g << 1) | ch);
                     tmem_st16_fill(tbase + ch * 16, magic4);             // re-arm, completes under the arithmetic
                     rescale16(vc, ch);
