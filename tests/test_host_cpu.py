@@ -167,6 +167,13 @@ def test_argument_errors_before_any_launch():
     assert lib.ade_b200_factored(ctypes.byref(d), 16, 16, 16, 16, 16, 1 << 20, 4, None) == -1    # both base terms
     assert lib.ade_b200_factored(ctypes.byref(d), 16, 16, None, 16, 16, 1 << 20, 129, None) == -2  # T too large
     assert lib.ade_b200_factored(ctypes.byref(d), 16, 16, None, 16, 16, 64, 4, None) == -4        # scratch too small
+    # expanded operands of the reconstruction: both arrays are required and 16-byte aligned; the delta is checked first
+    assert lib.ade_b200_expand_codes(ctypes.byref(d), None, 32, None) == -1
+    assert lib.ade_b200_expand_codes(ctypes.byref(d), 16, 40, None) == -3
+    assert lib.ade_b200_recon_expanded(ctypes.byref(d), None, None, 16, 32, None, None, None) == -1
+    assert lib.ade_b200_recon_expanded(ctypes.byref(d), 24, 32, 16, 32, None, None, None) == -3
+    assert lib.ade_b200_recon_expanded(None, 16, 32, 16, 32, None, None, None) == -1
+    assert lib.ade_b200_set_option(99, 0) == -2 and lib.ade_b200_set_option(_lib.OPT_ATTN_SINGLE_PASS, 1) == 0
     with pytest.raises(ValueError):
         kernels.pack_int4({"U_codes": torch.zeros(8, 96, dtype=torch.uint8), "Vt_codes": torch.zeros(96, 8, dtype=torch.uint8)})
 
