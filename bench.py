@@ -561,6 +561,20 @@ def run_ade(args):
     pk[1].record()
     torch.cuda.synchronize()
     recon_packed_us = pk[0].elapsed_time(pk[1]) * 1e3 / (len(mods) + 1)
+    # ... and the whole step that way (a few steps, for the record: the headline keeps the operands)
+    def step_unpacking():
+        for m, x in zip(mods, xs_dev):
+            torch.nn.functional.linear(x, kernels.recon_int4(m._stored_form(), m.weight))
+    for _ in range(2):
+        step_unpacking()
+    pk2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    n_alt = min(args.steps, 10)
+    pk2[0].record()
+    for _ in range(n_alt):
+        step_unpacking()
+    pk2[1].record()
+    torch.cuda.synchronize()
+    ms_step_unpacking = pk2[0].elapsed_time(pk2[1]) / n_alt
 
     # ---- end to end through the module API, host buffers in and out
     for i in range(4):
@@ -649,6 +663,7 @@ def run_ade(args):
                          "peak_kind": peak_kind, "kernel": "recon_strip_kernel (int8 operands expanded once per module and kept; "
                          "algorithmic bytes count the packed codes)", "us_per_launch": recon_ms * 1e3,
                          "us_per_launch_unpacking_in_kernel": recon_packed_us,
+                         "ms_per_step_unpacking_in_kernel": ms_step_unpacking,
                          "int8_tops_kernel_only": (WORK_OPS / 3) / (recon_ms * 1e-3) / 1e12},
             "cpu_baseline": {"value": cpu_tops, "unit": UNIT, "cores": cpu_threads, "blas_threads": blas, "kind": "port",
                              "sample": f"{cpu_rows} of 11008 rows of gate_proj: reconstruct + base add + x W'^T, median of 5, {cpu_sec:.2f} s per pass"},
