@@ -426,20 +426,33 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
         }
         return a;
     };
-    for (int base = 0; base < pend; base += U * G) {
-        uint4 kq[U], vq[U];
-        bool on[U];
+    // Rows base + u G + grp, u = 0 .. U - 1, form a batch.  The k rows of the next batch are requested as soon as the
+    // scores of the current one have been formed (their registers are free then) and its v rows once the current ones
+    // have been accumulated, so loads are in flight under both halves of the arithmetic.
+    uint4 kq[U], vq[U];
+    uint32_t onm = 0;                                       // bit u: row u of the batch is attended to and comes from the cache
+    auto rows_on = [&](int base) {
+        uint32_t mk = 0;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int pp = base + u * G + grp;
-            on[u] = pp < pend && pp != p0 && (mb ? mb[pp] : true);      // the new token's row comes from registers below
-            kq[u] = make_uint4(0u, 0u, 0u, 0u);
-            vq[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (on[u]) {
-                kq[u] = krow[static_cast<size_t>(pp) * CH];
-                vq[u] = vrow[static_cast<size_t>(pp) * CH];
-            }
+            if (pp < pend && pp != p0 && (mb ? mb[pp] : true)) mk |= 1u << u;      // the new token's row comes from registers below
         }
+        return mk;
+    };
+    auto load_rows = [&](uint4 (&dst)[U], const uint4* rows, int base, uint32_t mk) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            dst[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (mk >> u & 1u) dst[u] = rows[static_cast<size_t>(base + u * G + grp) * CH];
+        }
+    };
+    if (pend > 0) {
+        onm = rows_on(0);
+        load_rows(kq, krow, 0, onm);
+        load_rows(vq, vrow, 0, onm);
+    }
+    for (int base = 0; base < pend; base += U * G) {
         float sv[U];
         float bm = -3.0e38f;
 #pragma unroll
@@ -447,9 +460,12 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
             float a = dot8(kq[u]);
 #pragma unroll
             for (int o = CH >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
-            sv[u] = on[u] ? a * scale : -3.0e38f;
+            sv[u] = (onm >> u & 1u) ? a * scale : -3.0e38f;
             bm = fmaxf(bm, sv[u]);
         }
+        const int nbase = base + U * G;
+        const uint32_t onn = nbase < pend ? rows_on(nbase) : 0u;
+        if (nbase < pend) load_rows(kq, krow, nbase, onn);
         if (bm > -1.0e38f) {                                // uniform over the group's lanes
             const float mn = fmaxf(m, bm);
             const float f = expf(m - mn);                   // 0 for the first rows of the group
@@ -458,7 +474,7 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
             for (int i = 0; i < 8; ++i) acc[i] *= f;
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const float w = on[u] ? expf(sv[u] - mn) : 0.f;
+                const float w = (onm >> u & 1u) ? expf(sv[u] - mn) : 0.f;
                 l += w;
                 const uint32_t ww[4] = {vq[u].x, vq[u].y, vq[u].z, vq[u].w};
 #pragma unroll
@@ -469,6 +485,8 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
             }
             m = mn;
         }
+        if (nbase < pend) load_rows(vq, vrow, nbase, onn);
+        onm = onn;
     }
     // the new token itself (its k and v have not been read back from the cache): row group 0
     {
