@@ -392,40 +392,11 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
     const __nv_bfloat16* vr = v + static_cast<size_t>(b) * v_stride + kvh * hd;
     __nv_bfloat16* kcb = kc + (static_cast<size_t>(b) * hk + kvh) * L * hd;
     __nv_bfloat16* vcb = vc + (static_cast<size_t>(b) * hk + kvh) * L * hd;
-    for (int d = tid; d < hd; d += 128) {
-        const float c = __bfloat162float(cs[static_cast<size_t>(b) * cs_batch_stride + d]);
-        const float s = __bfloat162float(sn[static_cast<size_t>(b) * cs_batch_stride + d]);
-        const int od = d < half ? d + half : d - half;
-        const float sign = d < half ? -1.f : 1.f;
-        qs[d] = bf16r(bf16r(__bfloat162float(qr[d]) * c) + bf16r(sign * __bfloat162float(qr[od]) * s));
-        kn[d] = bf16r(bf16r(__bfloat162float(kr[d]) * c) + bf16r(sign * __bfloat162float(kr[od]) * s));
-        vn[d] = __bfloat162float(vr[d]);
-        if (h % group == 0 && p0 >= 0 && p0 < L) {
-            kcb[static_cast<size_t>(p0) * hd + d] = __float2bfloat16_rn(kn[d]);
-            vcb[static_cast<size_t>(p0) * hd + d] = vr[d];
-        }
-    }
-    __syncthreads();
     const int c8 = tid % CH, grp = tid / CH;
-    float qv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) qv[i] = qs[c8 * 8 + i];
     const bool* mb = mask ? mask + static_cast<size_t>(b) * mask_stride : nullptr;
     const int pend = mb ? L : min(p0 + 1, L);              // positions to look at (without a mask: 0 .. *pos)
     const uint4* krow = reinterpret_cast<const uint4*>(kcb) + c8;
     const uint4* vrow = reinterpret_cast<const uint4*>(vcb) + c8;
-    float m = -3.0e38f, l = 0.f;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    auto dot8 = [&](const uint4& w) {
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-        float a = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            a += qv[2 * e] * __uint_as_float(ww[e] << 16);
-            a += qv[2 * e + 1] * __uint_as_float(ww[e] & 0xFFFF0000u);
-        }
-        return a;
-    };
     // Rows base + u G + grp, u = 0 .. U - 1, form a batch.  The k rows of the next batch are requested as soon as the
     // scores of the current one have been formed (their registers are free then) and its v rows once the current ones
     // have been accumulated, so loads are in flight under both halves of the arithmetic.
@@ -447,11 +418,40 @@ __global__ void __launch_bounds__(128) attn_decode_stream_kernel(const __nv_bflo
             if (mk >> u & 1u) dst[u] = rows[static_cast<size_t>(base + u * G + grp) * CH];
         }
     };
-    if (pend > 0) {
+    if (pend > 0) {                                         // the first batch travels while q and k are being rotated
         onm = rows_on(0);
         load_rows(kq, krow, 0, onm);
         load_rows(vq, vrow, 0, onm);
     }
+    for (int d = tid; d < hd; d += 128) {
+        const float c = __bfloat162float(cs[static_cast<size_t>(b) * cs_batch_stride + d]);
+        const float s = __bfloat162float(sn[static_cast<size_t>(b) * cs_batch_stride + d]);
+        const int od = d < half ? d + half : d - half;
+        const float sign = d < half ? -1.f : 1.f;
+        qs[d] = bf16r(bf16r(__bfloat162float(qr[d]) * c) + bf16r(sign * __bfloat162float(qr[od]) * s));
+        kn[d] = bf16r(bf16r(__bfloat162float(kr[d]) * c) + bf16r(sign * __bfloat162float(kr[od]) * s));
+        vn[d] = __bfloat162float(vr[d]);
+        if (h % group == 0 && p0 >= 0 && p0 < L) {
+            kcb[static_cast<size_t>(p0) * hd + d] = __float2bfloat16_rn(kn[d]);
+            vcb[static_cast<size_t>(p0) * hd + d] = vr[d];
+        }
+    }
+    __syncthreads();
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = qs[c8 * 8 + i];
+    float m = -3.0e38f, l = 0.f;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto dot8 = [&](const uint4& w) {
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        float a = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            a += qv[2 * e] * __uint_as_float(ww[e] << 16);
+            a += qv[2 * e + 1] * __uint_as_float(ww[e] & 0xFFFF0000u);
+        }
+        return a;
+    };
     for (int base = 0; base < pend; base += U * G) {
         float sv[U];
         float bm = -3.0e38f;
